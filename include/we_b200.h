@@ -1,0 +1,174 @@
+/*
+ * we_b200.h -- C ABI of libwe_b200.so: frame-causal attention over the KV
+ * ring-buffer cache, hand-written for NVIDIA B200 (sm_100a).
+ *
+ * The reference (Overworldai/world_engine) is a pure-Python PyTorch library
+ * with no FFI of its own; each entry point below names the Python code whose
+ * work it replaces (paths relative to the reference project root).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its name ends in `_host`.
+ *   - The library owns no memory and keeps no session state: caches,
+ *     `written` vectors, workspaces and status words belong to the caller.
+ *   - All work is enqueued on `stream` (a cudaStream_t passed as void*);
+ *     nothing synchronises with the host, so calls may be captured in a
+ *     CUDA graph.  `frame_t` is read on the device for the same reason
+ *     (reference: src/model/kv_cache.py:126 keeps it a device scalar).
+ *   - Return value: 0 = OK; negative = argument rejected on the host before
+ *     any launch (WE_B200_E_*); positive = the cudaError_t of a failed
+ *     launch.  Nothing throws, aborts or traps.  Device-side anomalies (a
+ *     bounded wait that expired) are written to `*status` and the kernel
+ *     returns; 0 there means healthy.
+ *   - Strides are in ELEMENTS.  The innermost (head_dim) axis is contiguous.
+ *   - dtype codes: WE_B200_BF16, WE_B200_F16 (attention + append),
+ *     WE_B200_F32 (append only).
+ *
+ * Cache geometry (one layer), exactly the reference's LayerKVCache
+ * (src/model/kv_cache.py:70-97): ring of L tokens + one tail frame of T
+ * tokens, capacity C = L + T.  Element (plane, b, h, token, d) of `kv` lives
+ * at  plane*kv_plane_stride + b*kv_batch_stride + (h*C + token)*Dh + d.
+ * The reference tensor kv[2,B,H,C,Dh] has kv_plane_stride = B*H*C*Dh and
+ * kv_batch_stride = H*C*Dh; a slab of independent sessions [S,2,1,H,C,Dh]
+ * has kv_plane_stride = H*C*Dh and kv_batch_stride = 2*H*C*Dh.
+ * `written` is C bytes (0/1) per batch row, rows `written_batch_stride`
+ * bytes apart (0 = one vector shared by all rows, as in the reference).
+ * `frame_t` is an int64 per batch row, rows `frame_t_stride` elements apart
+ * (0 = row 0's value for every row, as src/model/kv_cache.py:126 does).
+ */
+#ifndef WE_B200_H_
+#define WE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WE_B200_ABI_VERSION 1
+
+enum {
+  WE_B200_BF16 = 0,
+  WE_B200_F16 = 1,
+  WE_B200_F32 = 2
+};
+
+enum {
+  WE_B200_OK = 0,
+  WE_B200_E_NULL = -1,        /* a required pointer is null                     */
+  WE_B200_E_ALIGN = -2,       /* a pointer or stride is not 16-byte aligned      */
+  WE_B200_E_SHAPE = -3,       /* L % T != 0, T > L, dilation does not divide...  */
+  WE_B200_E_DTYPE = -4,       /* dtype / head_dim unsupported by this kernel     */
+  WE_B200_E_WORKSPACE = -5,   /* workspace missing or too small                  */
+  WE_B200_E_DRIVER = -6,      /* tensor-map encoder unavailable / encode failed  */
+  WE_B200_E_LIMIT = -7        /* a size exceeds a documented maximum             */
+};
+
+/* Device status codes written to *status by the attention kernel. */
+enum {
+  WE_B200_ST_OK = 0,
+  WE_B200_ST_WAIT_EXPIRED = 1  /* a bounded mbarrier wait gave up; output invalid */
+};
+
+typedef struct we_b200_cache_geom {
+  int32_t B;                    /* batch rows (independent sessions)            */
+  int32_t Hkv;                  /* kv heads                                      */
+  int32_t T;                    /* tokens per frame                              */
+  int32_t Dh;                   /* head dim                                      */
+  int64_t L;                    /* ring length in tokens (multiple of T)         */
+  int32_t dilation;             /* pinned_dilation, >= 1                         */
+  int32_t dtype;                /* WE_B200_*                                     */
+  int64_t kv_plane_stride;      /* elements between the K and the V plane        */
+  int64_t kv_batch_stride;      /* elements between batch rows                   */
+  int64_t written_batch_stride; /* bytes between batch rows of `written`         */
+  int64_t frame_t_stride;       /* int64 elements between batch rows of frame_t  */
+} we_b200_cache_geom;
+
+/* ABI version of the loaded library (== WE_B200_ABI_VERSION of its build). */
+int we_b200_abi_version(void);
+
+/* Static message for a return code of this library (or the CUDA runtime). */
+const char* we_b200_strerror(int code);
+
+/*
+ * Fused K/V append.  Replaces torch.stack + the two index_copy_ calls and the
+ * `written` / mask bookkeeping of LayerKVCache.upsert
+ * (src/model/kv_cache.py:126-151,191-193):
+ *   - always copies the new frame into the tail slice [L, L+T)        (:138)
+ *   - if !is_frozen and frame_t % dilation == 0, copies it into ring slot
+ *     base = ((frame_t + d-1)/d % ((L/T)/d)) * T and sets written there
+ *                                                              (:129-131,147-151)
+ *   - if mask_written != NULL, writes the per-token visibility of this call
+ *     (written with the ring slot hidden on write steps)           (:141-143)
+ * k_new / v_new are [B,Hkv,T,Dh] views with strides (b,h,t) in elements.
+ * One read of the new frame, 16-byte vector stores.
+ */
+int we_b200_kv_append(const void* k_new, const int64_t* k_strides_host,
+                      const void* v_new, const int64_t* v_strides_host,
+                      void* kv, uint8_t* written, uint8_t* mask_written,
+                      const int64_t* frame_t, const we_b200_cache_geom* geom_host,
+                      int is_frozen, void* stream);
+
+/*
+ * Block-mask tables.  Replaces make_block_mask's tensor bookkeeping
+ * (src/model/kv_cache.py:18-45): classifies each 128-token KV block of
+ * mask_written[C] as empty / partial / full and emits flex-attention's
+ * ordered form (indices of set blocks ascending, then the rest ascending --
+ * what a stable descending argsort of the bool row yields).
+ * Outputs are int32: *_num_blocks[q_blocks], *_indices[q_blocks*kv_blocks],
+ * q_blocks = ceil(T/128), kv_blocks = ceil(C/128).
+ */
+int we_b200_block_mask(const uint8_t* mask_written, int64_t C, int32_t T,
+                       int32_t* kv_num_blocks, int32_t* kv_indices,
+                       int32_t* full_kv_num_blocks, int32_t* full_kv_indices,
+                       void* stream);
+
+/*
+ * Bytes of zero-initialised workspace we_b200_frame_attn needs for this
+ * shape on the current device (split-KV partials + arrival counters).  The
+ * kernel leaves the counters at zero again, so one allocation zeroed once
+ * serves every later call of the same or a smaller shape.
+ */
+size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh, int64_t L);
+
+/*
+ * Frame-causal attention over the cache.  Replaces
+ * flex_attention(q, k_full, v_full, block_mask=bm, enable_gqa=...) at
+ * src/model/attn.py:116 / src/patch_model.py:133 together with the BlockMask
+ * of src/model/kv_cache.py:141-144.  Must run after we_b200_kv_append of the
+ * same frame on the same stream.  The T queries of the new frame attend to
+ * every token with written != 0, except the ring slot this frame maps to
+ * when frame_t % dilation == 0, plus the tail frame; wrap-around is index
+ * arithmetic, nothing is gathered.  q / out are [B,Hq,T,Dh] views with
+ * strides (b,h,t) in elements; Hq % Hkv == 0 (GQA by head broadcast).
+ * scale <= 0 selects 1/sqrt(Dh).  bf16 / f16, Dh in {64, 128}.
+ */
+int we_b200_frame_attn(const void* q, const int64_t* q_strides_host,
+                       void* out, const int64_t* out_strides_host, int32_t Hq,
+                       const void* kv, const uint8_t* written, const int64_t* frame_t,
+                       const we_b200_cache_geom* geom_host, float scale,
+                       void* workspace, size_t workspace_bytes,
+                       int32_t* status, void* stream);
+
+/*
+ * we_b200_kv_append followed by we_b200_frame_attn on `stream`: one call per
+ * layer-step, what Attn.forward does at src/model/attn.py:113-116.
+ */
+int we_b200_append_attend(const void* q, const int64_t* q_strides_host,
+                          void* out, const int64_t* out_strides_host, int32_t Hq,
+                          const void* k_new, const int64_t* k_strides_host,
+                          const void* v_new, const int64_t* v_strides_host,
+                          void* kv, uint8_t* written, uint8_t* mask_written,
+                          const int64_t* frame_t, const we_b200_cache_geom* geom_host,
+                          int is_frozen, float scale,
+                          void* workspace, size_t workspace_bytes,
+                          int32_t* status, void* stream);
+
+/* Number of kernels the previous three entry points have launched in this
+ * process (diagnostic counter for benchmarks; relaxed atomics). */
+uint64_t we_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WE_B200_H_ */

@@ -1,0 +1,99 @@
+"""Frame-causal self-attention module and its installer.
+
+The reference swaps modules in place: `apply_inference_patches` walks the
+model and calls `model.set_submodule(name, Replacement(old, ...))`
+(src/patch_model.py:144-147,182-185).  `patch_Attn_b200` is one more function
+of that chain.  It replaces every self-attention module (`Attn`,
+src/model/attn.py:70-122, or its merged-QKV form `MergedQKVAttn`,
+src/patch_model.py:92-141) by `B200Attn`, whose forward keeps the projections,
+value residual, QK-norm, RoPE, head gate and output projection of the original
+and hands the cache update + attention to the sm_100a library in one call.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .kv_cache import B200StaticKVCache
+
+
+def _unit_rms(x: torch.Tensor) -> torch.Tensor:
+    # weightless RMS norm over the head dim (src/model/nn.py:55-56)
+    return F.rms_norm(x, (x.size(-1),))
+
+
+class B200Attn(nn.Module):
+    """Drop-in for Attn / MergedQKVAttn with the same forward signature
+    `(x, pos_ids, v1, kv_cache) -> (y, v1)` (src/model/world_model.py:166)."""
+
+    def __init__(self, src: nn.Module):
+        super().__init__()
+        self.layer_idx = src.layer_idx
+        self.n_heads = src.n_heads
+        self.n_kv_heads = src.n_kv_heads
+        self.d_head = src.d_head
+        self.value_residual = bool(getattr(src, "value_residual", False))
+        self.gated_attn = bool(getattr(src, "gated_attn", False))
+        if self.value_residual:
+            self.v_lamb = src.v_lamb
+        if self.gated_attn:
+            self.gate_proj = src.gate_proj
+        self.rope = src.rope
+        self.out_proj = src.out_proj
+        self.q_out = self.n_heads * self.d_head
+        self.kv_out = self.n_kv_heads * self.d_head
+        if hasattr(src, "qkv_proj"):
+            self.qkv_proj = src.qkv_proj
+        else:
+            # merge the three projections the way src/patch_model.py:102-112 does
+            w = src.q_proj.weight
+            self.qkv_proj = nn.Linear(src.q_proj.in_features, self.q_out + 2 * self.kv_out, bias=False,
+                                      device=w.device, dtype=w.dtype)
+            with torch.no_grad():
+                self.qkv_proj.weight.copy_(torch.cat(
+                    [src.q_proj.weight, src.k_proj.weight, src.v_proj.weight], dim=0))
+        self.train(src.training)
+
+    def forward(self, x, pos_ids, v1, kv_cache: B200StaticKVCache):
+        B, T = x.shape[:2]
+        q, k, v = self.qkv_proj(x).split((self.q_out, self.kv_out, self.kv_out), dim=-1)
+        q = q.reshape(B, T, self.n_heads, self.d_head).transpose(1, 2)
+        k = k.reshape(B, T, self.n_kv_heads, self.d_head).transpose(1, 2)
+        v = v.reshape(B, T, self.n_kv_heads, self.d_head).transpose(1, 2)
+
+        if self.value_residual:
+            v1 = v if v1 is None else v1
+            v = torch.lerp(v, v1.view_as(v), self.v_lamb)
+
+        q, k = _unit_rms(q), _unit_rms(k)
+        q, k = self.rope(q, pos_ids), self.rope(k, pos_ids)
+
+        # cache update + attention: replaces upsert + flex_attention
+        # (src/patch_model.py:131-133)
+        y = kv_cache.append_and_attend(q, k, v, pos_ids, self.layer_idx)
+
+        if self.gated_attn:
+            gates = torch.sigmoid(self.gate_proj(x[..., : self.n_heads]))
+            y = y * gates.permute(0, 2, 1).unsqueeze(-1)
+
+        y = y.transpose(1, 2).reshape(B, T, -1)
+        return self.out_proj(y), v1
+
+
+def _is_self_attention(mod: nn.Module) -> bool:
+    if isinstance(mod, B200Attn):
+        return False
+    names = {c.__name__ for c in type(mod).__mro__}
+    return "Attn" in names  # Attn and its subclass MergedQKVAttn; CrossAttention is a different class
+
+
+def patch_Attn_b200(model: nn.Module) -> None:
+    """Installs B200Attn on every self-attention module of `model`.  Call it
+    after (or instead of) the reference's patch_Attn_merge_qkv; the engine must
+    then own a B200StaticKVCache."""
+    for name, mod in list(model.named_modules()):
+        if _is_self_attention(mod):
+            model.set_submodule(name, B200Attn(mod))

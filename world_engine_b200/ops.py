@@ -1,0 +1,224 @@
+"""Tensor-level entry points over the C ABI, plus their `torch.library` custom
+ops so that the calls survive `torch.compile(fullgraph=True)` -- the way the
+reference wraps its own native kernel (src/quantize.py:17-42).
+
+Every function here enqueues on the caller's current CUDA stream, performs no
+host synchronisation and allocates nothing except (once per device) the
+split-KV workspace and the status word.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import CacheGeom, Strides3
+
+_DTYPE_CODE = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"world_engine_b200: unsupported cache dtype {dtype}") from None
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "world_engine_b200 runs on CUDA tensors only (sm_100a); there is no CPU path")
+
+
+def _strides3(t: torch.Tensor) -> Strides3:
+    if t.dim() != 4 or t.stride(3) != 1:
+        raise ValueError("expected a [B, H, T, Dh] tensor whose last axis is contiguous")
+    return Strides3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def make_geom(kv: torch.Tensor, written: torch.Tensor, tokens_per_frame: int, dilation: int,
+              frame_t_stride: int = 0) -> CacheGeom:
+    """Geometry of a reference-layout cache tensor kv[2, B, H, L+T, Dh]
+    (src/model/kv_cache.py:81-84)."""
+    if kv.dim() != 5 or kv.size(0) != 2:
+        raise ValueError("kv must be [2, B, H, L + tokens_per_frame, Dh]")
+    if kv.stride(4) != 1 or kv.stride(3) != kv.size(4) or kv.stride(2) != kv.size(3) * kv.size(4):
+        raise ValueError("kv must be contiguous over (head, token, head_dim)")
+    _, B, H, C, Dh = kv.shape
+    g = CacheGeom()
+    g.B, g.Hkv, g.T, g.Dh = B, H, tokens_per_frame, Dh
+    g.L = C - tokens_per_frame
+    g.dilation = dilation
+    g.dtype = dtype_code(kv.dtype)
+    g.kv_plane_stride = kv.stride(0)
+    g.kv_batch_stride = kv.stride(1)
+    g.written_batch_stride = written.stride(0) if written.dim() == 2 else 0
+    g.frame_t_stride = frame_t_stride
+    return g
+
+
+# ------------------------------------------------------------------ workspace
+_workspaces = {}
+_status_words = {}
+
+
+def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised split-KV workspace of the device (grown on demand).
+    Calls that share it must be ordered on one stream."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    st = _status_words.get(key)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = st
+    return st
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising health check: raises if a kernel on `device` gave up on a bounded wait."""
+    st = int(status_word(device).item())
+    if st != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f"world_engine_b200: attention kernel reported device status {st} "
+                           "(a bounded wait expired; the output of that call is invalid)")
+
+
+# ------------------------------------------------------------------ raw calls
+def kv_append_(kv: torch.Tensor, written: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+               frame_t: torch.Tensor, tokens_per_frame: int, dilation: int, is_frozen: bool,
+               mask_written: Optional[torch.Tensor] = None, frame_t_stride: int = 0) -> None:
+    """In-place append of one frame (we_b200_kv_append)."""
+    _require_cuda(kv, written, k_new, v_new, frame_t, mask_written)
+    g = make_geom(kv, written, tokens_per_frame, dilation, frame_t_stride)
+    lib = _lib.load()
+    with torch.cuda.device(kv.device):
+        rc = lib.we_b200_kv_append(
+            k_new.data_ptr(), _strides3(k_new), v_new.data_ptr(), _strides3(v_new),
+            kv.data_ptr(), written.data_ptr(),
+            mask_written.data_ptr() if mask_written is not None else None,
+            frame_t.data_ptr(), ctypes.byref(g), int(bool(is_frozen)), _stream_ptr(kv.device))
+    _lib.check(rc, "we_b200_kv_append")
+
+
+def frame_attn(q: torch.Tensor, kv: torch.Tensor, written: torch.Tensor, frame_t: torch.Tensor,
+               tokens_per_frame: int, dilation: int, scale: float = 0.0,
+               out: Optional[torch.Tensor] = None, frame_t_stride: int = 0) -> torch.Tensor:
+    """Attention of the new frame's queries over the cache (we_b200_frame_attn).
+    The output has q's shape and strides, like flex_attention's."""
+    _require_cuda(q, kv, written, frame_t)
+    g = make_geom(kv, written, tokens_per_frame, dilation, frame_t_stride)
+    if out is None:
+        out = torch.empty_like(q)
+    lib = _lib.load()
+    B, Hq, T, Dh = q.shape
+    with torch.cuda.device(q.device):
+        need = lib.we_b200_attn_workspace_bytes(B, Hq, T, Dh, g.L)
+        ws = workspace_for(q.device, need)
+        rc = lib.we_b200_frame_attn(
+            q.data_ptr(), _strides3(q), out.data_ptr(), _strides3(out), Hq,
+            kv.data_ptr(), written.data_ptr(), frame_t.data_ptr(), ctypes.byref(g), float(scale),
+            ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "we_b200_frame_attn")
+    return out
+
+
+def append_attend(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv: torch.Tensor,
+                  written: torch.Tensor, frame_t: torch.Tensor, tokens_per_frame: int, dilation: int,
+                  is_frozen: bool, scale: float = 0.0, out: Optional[torch.Tensor] = None,
+                  mask_written: Optional[torch.Tensor] = None, frame_t_stride: int = 0) -> torch.Tensor:
+    """One layer-step: append the frame, then attend (we_b200_append_attend)."""
+    _require_cuda(q, k_new, v_new, kv, written, frame_t, mask_written)
+    g = make_geom(kv, written, tokens_per_frame, dilation, frame_t_stride)
+    if out is None:
+        out = torch.empty_like(q)
+    lib = _lib.load()
+    B, Hq, T, Dh = q.shape
+    with torch.cuda.device(q.device):
+        need = lib.we_b200_attn_workspace_bytes(B, Hq, T, Dh, g.L)
+        ws = workspace_for(q.device, need)
+        rc = lib.we_b200_append_attend(
+            q.data_ptr(), _strides3(q), out.data_ptr(), _strides3(out), Hq,
+            k_new.data_ptr(), _strides3(k_new), v_new.data_ptr(), _strides3(v_new),
+            kv.data_ptr(), written.data_ptr(),
+            mask_written.data_ptr() if mask_written is not None else None,
+            frame_t.data_ptr(), ctypes.byref(g), int(bool(is_frozen)), float(scale),
+            ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "we_b200_append_attend")
+    return out
+
+
+def block_mask_tables(mask_written: torch.Tensor, tokens_per_frame: int
+                      ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """int32 tables of the flex BlockMask for a visibility vector (we_b200_block_mask)."""
+    _require_cuda(mask_written)
+    C = mask_written.numel()
+    qb = (tokens_per_frame + 127) // 128
+    kb = (C + 127) // 128
+    dev = mask_written.device
+    kv_num = torch.empty((1, 1, qb), dtype=torch.int32, device=dev)
+    kv_idx = torch.empty((1, 1, qb, kb), dtype=torch.int32, device=dev)
+    full_num = torch.empty((1, 1, qb), dtype=torch.int32, device=dev)
+    full_idx = torch.empty((1, 1, qb, kb), dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.we_b200_block_mask(mask_written.data_ptr(), C, tokens_per_frame, kv_num.data_ptr(),
+                                    kv_idx.data_ptr(), full_num.data_ptr(), full_idx.data_ptr(),
+                                    _stream_ptr(dev))
+    _lib.check(rc, "we_b200_block_mask")
+    return kv_num, kv_idx, full_num, full_idx
+
+
+# ----------------------------------------------------------------- custom ops
+# Registered under the reference's own namespace style ("world_engine::...").
+@torch.library.custom_op("world_engine_b200::append_attend", mutates_args=("kv", "written"))
+def append_attend_op(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv: torch.Tensor,
+                     written: torch.Tensor, frame_t: torch.Tensor, tokens_per_frame: int,
+                     dilation: int, is_frozen: bool, scale: float) -> torch.Tensor:
+    return append_attend(q, k_new, v_new, kv, written, frame_t, tokens_per_frame, dilation,
+                         is_frozen, scale)
+
+
+@append_attend_op.register_fake
+def _append_attend_fake(q, k_new, v_new, kv, written, frame_t, tokens_per_frame, dilation,
+                        is_frozen, scale):
+    return torch.empty_like(q)
+
+
+@torch.library.custom_op("world_engine_b200::kv_append", mutates_args=("kv", "written", "mask_written"))
+def kv_append_op(kv: torch.Tensor, written: torch.Tensor, mask_written: torch.Tensor,
+                 k_new: torch.Tensor, v_new: torch.Tensor, frame_t: torch.Tensor,
+                 tokens_per_frame: int, dilation: int, is_frozen: bool) -> None:
+    kv_append_(kv, written, k_new, v_new, frame_t, tokens_per_frame, dilation, is_frozen,
+               mask_written=mask_written)
+
+
+@kv_append_op.register_fake
+def _kv_append_fake(kv, written, mask_written, k_new, v_new, frame_t, tokens_per_frame, dilation,
+                    is_frozen):
+    return None
+
+
+@torch.library.custom_op("world_engine_b200::frame_attn", mutates_args=())
+def frame_attn_op(q: torch.Tensor, kv: torch.Tensor, written: torch.Tensor, frame_t: torch.Tensor,
+                  tokens_per_frame: int, dilation: int, scale: float) -> torch.Tensor:
+    return frame_attn(q, kv, written, frame_t, tokens_per_frame, dilation, scale)
+
+
+@frame_attn_op.register_fake
+def _frame_attn_fake(q, kv, written, frame_t, tokens_per_frame, dilation, scale):
+    return torch.empty_like(q)
