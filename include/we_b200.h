@@ -47,6 +47,12 @@ extern "C" {
 
 #define WE_B200_ABI_VERSION 1
 
+#if defined(__GNUC__)
+#define WE_B200_API __attribute__((visibility("default")))
+#else
+#define WE_B200_API
+#endif
+
 enum {
   WE_B200_BF16 = 0,
   WE_B200_F16 = 1,
@@ -85,10 +91,10 @@ typedef struct we_b200_cache_geom {
 } we_b200_cache_geom;
 
 /* ABI version of the loaded library (== WE_B200_ABI_VERSION of its build). */
-int we_b200_abi_version(void);
+WE_B200_API int we_b200_abi_version(void);
 
 /* Static message for a return code of this library (or the CUDA runtime). */
-const char* we_b200_strerror(int code);
+WE_B200_API const char* we_b200_strerror(int code);
 
 /*
  * Fused K/V append.  Replaces torch.stack + the two index_copy_ calls and the
@@ -103,7 +109,7 @@ const char* we_b200_strerror(int code);
  * k_new / v_new are [B,Hkv,T,Dh] views with strides (b,h,t) in elements.
  * One read of the new frame, 16-byte vector stores.
  */
-int we_b200_kv_append(const void* k_new, const int64_t* k_strides_host,
+WE_B200_API int we_b200_kv_append(const void* k_new, const int64_t* k_strides_host,
                       const void* v_new, const int64_t* v_strides_host,
                       void* kv, uint8_t* written, uint8_t* mask_written,
                       const int64_t* frame_t, const we_b200_cache_geom* geom_host,
@@ -118,7 +124,7 @@ int we_b200_kv_append(const void* k_new, const int64_t* k_strides_host,
  * Outputs are int32: *_num_blocks[q_blocks], *_indices[q_blocks*kv_blocks],
  * q_blocks = ceil(T/128), kv_blocks = ceil(C/128).
  */
-int we_b200_block_mask(const uint8_t* mask_written, int64_t C, int32_t T,
+WE_B200_API int we_b200_block_mask(const uint8_t* mask_written, int64_t C, int32_t T,
                        int32_t* kv_num_blocks, int32_t* kv_indices,
                        int32_t* full_kv_num_blocks, int32_t* full_kv_indices,
                        void* stream);
@@ -129,7 +135,7 @@ int we_b200_block_mask(const uint8_t* mask_written, int64_t C, int32_t T,
  * kernel leaves the counters at zero again, so one allocation zeroed once
  * serves every later call of the same or a smaller shape.
  */
-size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh, int64_t L);
+WE_B200_API size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh, int64_t L);
 
 /*
  * Frame-causal attention over the cache.  Replaces
@@ -143,7 +149,7 @@ size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh
  * strides (b,h,t) in elements; Hq % Hkv == 0 (GQA by head broadcast).
  * scale <= 0 selects 1/sqrt(Dh).  bf16 / f16, Dh in {64, 128}.
  */
-int we_b200_frame_attn(const void* q, const int64_t* q_strides_host,
+WE_B200_API int we_b200_frame_attn(const void* q, const int64_t* q_strides_host,
                        void* out, const int64_t* out_strides_host, int32_t Hq,
                        const void* kv, const uint8_t* written, const int64_t* frame_t,
                        const we_b200_cache_geom* geom_host, float scale,
@@ -154,7 +160,7 @@ int we_b200_frame_attn(const void* q, const int64_t* q_strides_host,
  * we_b200_kv_append followed by we_b200_frame_attn on `stream`: one call per
  * layer-step, what Attn.forward does at src/model/attn.py:113-116.
  */
-int we_b200_append_attend(const void* q, const int64_t* q_strides_host,
+WE_B200_API int we_b200_append_attend(const void* q, const int64_t* q_strides_host,
                           void* out, const int64_t* out_strides_host, int32_t Hq,
                           const void* k_new, const int64_t* k_strides_host,
                           const void* v_new, const int64_t* v_strides_host,
@@ -166,7 +172,7 @@ int we_b200_append_attend(const void* q, const int64_t* q_strides_host,
 
 /* Number of kernels the previous three entry points have launched in this
  * process (diagnostic counter for benchmarks; relaxed atomics). */
-uint64_t we_b200_launch_count(void);
+WE_B200_API uint64_t we_b200_launch_count(void);
 
 #ifdef __cplusplus
 }

@@ -82,6 +82,11 @@ struct AttnParams {
   float* debug;                  // optional dump of the first S tile (debug builds)
 };
 
+#ifdef WE_ATTN_DEBUG
+// Debug builds only: descriptor fields overridable at run time (0 = keep the default).
+__constant__ uint32_t g_dbg[8];
+#endif
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if constexpr (BF16) {
@@ -276,10 +281,17 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // O += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16.
         const uint32_t d = tmem_base + kColO;
         const uint32_t a_t = tmem_base + ((i & 1) ? kColP1 : kColP0);
+        uint32_t v_lbo = Cfg::kChunkBytes, v_sbo = 1024, v_kstep = 2048, idesc_pv = kIdescPV;
+#ifdef WE_ATTN_DEBUG
+        if (g_dbg[0]) v_lbo = g_dbg[0];
+        if (g_dbg[1]) v_sbo = g_dbg[1];
+        if (g_dbg[2]) v_kstep = g_dbg[2];
+        if (g_dbg[3]) idesc_pv = g_dbg[3];
+#endif
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          const uint64_t bd = umma_desc_sw128(v_addr + st * Cfg::kTileBytes + kk * 2048, Cfg::kChunkBytes, 1024);
-          umma_ts(d, a_t + kk * 8, bd, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t bd = umma_desc_sw128(v_addr + st * Cfg::kTileBytes + kk * v_kstep, v_lbo, v_sbo);
+          umma_ts(d, a_t + kk * 8, bd, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&kv_empty[st]);
         tc_commit(o_ready);
@@ -658,6 +670,13 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
 }
 
 }  // namespace we
+
+#ifdef WE_ATTN_DEBUG
+extern "C" __attribute__((visibility("default"))) int we_b200_debug_set(int idx, uint32_t value) {
+  if (idx < 0 || idx >= 8) return -1;
+  return static_cast<int>(cudaMemcpyToSymbol(we::g_dbg, &value, sizeof(value), idx * sizeof(uint32_t)));
+}
+#endif
 
 extern "C" size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh, int64_t L) {
   if (B < 1 || Hq < 1 || T < 1 || Dh < 1 || L < 1) return 0;
