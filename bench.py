@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the frame-causal attention + KV ring-buffer append on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1 and per rank for N > 1): the single frame step at small-model
+scale -- B=1, H=16, head_dim=128, 256 tokens per frame, 16-frame ring that has
+wrapped (write pointer at slot 11), bf16, K/V append included.  One bench STEP
+is that layer-step run over 24 distinct layer caches (the 24 layers of one DiT
+forward; 24 x 35.65 MB of cache = 855 MB, far larger than L2, so every
+layer-step reads its K/V from HBM).  Sessions are independent, so N GPUs run N
+replicas of the workload with no collective on the data path (weak scaling);
+the only communication is the barrier and the max-over-ranks of the timing.
+
+Printed JSON line (rank 0): `value` = layer-steps per second over all ranks
+with inputs resident in HBM (CUDA-graph replay, CUDA events); `e2e` = the same
+through the public Python API with q/k/v coming from pinned HOST memory and
+the output read back every step; `roofline` = the attention kernel's
+algorithmic bytes per launch over its measured average launch duration against
+the measured HBM copy peak; `cpu_baseline` = the numpy oracle (a port of the
+reference's algorithm) timed on this box's host cores on a bounded sample.
+
+`--impl reference` times that CPU port alone (the reference itself is
+PyTorch code whose only implementation of this path on CPU is torch's eager
+flex_attention; its tree is not present on the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_LAYERS = 24
+FALLBACK_HBM_GBS = 6650.0
+WORKLOAD = ("cfg2: B=1 H=16 Dh=128 T=256, 16-frame ring wrapped (frame_t=27, slot 11), bf16, append included; "
+            "one step = 24 distinct layer caches (855 MB > L2, no flush needed)")
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thr = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                r = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                    "-i", str(self.gpu)], capture_output=True, text=True, timeout=5)
+                if r.returncode == 0 and r.stdout.strip():
+                    self.samples.append([x.strip() for x in r.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thr.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[1]))
+                mx.append(float(s[2]))
+            except Exception:
+                continue
+            for name, val in zip(names, s[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU port
+def cpu_layer_step_seconds(cfg, repeats: int):
+    """Times the oracle's layer-step (upsert + attention) on host cores.  Returns median seconds per layer-step."""
+    import numpy as np
+    from oracle import ring_attn_oracle as oracle   # CPU baseline leg: the one place bench.py may use oracle/
+    rng = np.random.default_rng(cfg.seed)
+    cache = oracle.OracleLayerKVCache(cfg.B, cfg.Hkv, cfg.L, cfg.Dh, np.uint16, cfg.T, cfg.dilation)
+    cache.kv[...] = oracle.f32_to_bf16_bits(rng.standard_normal(cache.kv.shape, dtype=np.float32))
+    cache.written[:] = True
+    q = oracle.round_to_bf16(rng.standard_normal((cfg.B, cfg.Hq, cfg.T, cfg.Dh), dtype=np.float32))
+    kv_new = oracle.f32_to_bf16_bits(rng.standard_normal((2, cfg.B, cfg.Hkv, cfg.T, cfg.Dh), dtype=np.float32))
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        k_full, v_full, mask = cache.upsert(kv_new, cfg.frame_t, True)
+        oracle.frame_attention(q, oracle.bf16_bits_to_f32(k_full), oracle.bf16_bits_to_f32(v_full), mask)
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), times
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference(args):
+    """`--impl reference`: the CPU port of the reference's path on this box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from world_engine_b200.synthetic import CONFIGS
+    cfg = CONFIGS["cfg2"]
+    cpu_layer_step_seconds(cfg, 2)                        # first calls pay page faults / BLAS thread start
+    probe, _ = cpu_layer_step_seconds(cfg, 2)
+    budget = 150.0                                        # seconds for the whole run
+    per_step = max(1, min(N_LAYERS, int(budget / max(probe, 1e-3) / max(1, args.steps + args.warmup))))
+    for _ in range(args.warmup):
+        cpu_layer_step_seconds(cfg, per_step)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_layer_step_seconds(cfg, per_step)
+    dt = time.perf_counter() - t0
+    value = per_step * args.steps / dt
+    cores = host_threads()
+    sample = f"{per_step} layer-step(s) of the cfg2 shape per step (numpy, fp32 math on bf16-rounded inputs)"
+    line = {
+        "impl": "reference", "metric": "frame-attn layer-steps/s (append + attention)", "value": value,
+        "unit": "layer-steps/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "layer_steps_per_step": per_step},
+        "us_per_layer_step": 1e6 / value,
+        "cpu_baseline": {"value": value, "unit": "layer-steps/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "layer-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# --------------------------------------------------------------------------- ours
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from world_engine_b200 import B200StaticKVCache, ops, _lib
+    from world_engine_b200.synthetic import CONFIGS
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback "
+                         "(use --impl reference for the CPU port)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    cfg = CONFIGS["cfg2"]
+
+    class ModelCfg:   # the reference's config keys that size the cache (src/model/kv_cache.py:161-179)
+        tokens_per_frame = cfg.T
+        local_window = cfg.ring_frames
+        global_window = cfg.ring_frames
+        global_attn_period = 1 << 30
+        global_attn_offset = 1
+        global_pinned_dilation = 1
+        n_heads = cfg.Hq
+        n_kv_heads = cfg.Hkv
+        d_model = cfg.Hq * cfg.Dh
+        n_layers = N_LAYERS
+
+    g = torch.Generator(device=dev).manual_seed(cfg.seed + rank)
+    cache = B200StaticKVCache(ModelCfg, batch_size=cfg.B, dtype=torch.bfloat16).to(dev)
+    for layer in cache.layers:
+        layer.kv.normal_(generator=g)
+        layer.written.fill_(True)
+        layer.validate = False
+    cache.set_frozen(True)
+    shape_q = (N_LAYERS, cfg.B, cfg.Hq, cfg.T, cfg.Dh)
+    shape_kv = (N_LAYERS, cfg.B, cfg.Hkv, cfg.T, cfg.Dh)
+    q = torch.randn(shape_q, device=dev, dtype=torch.bfloat16, generator=g)
+    k = torch.randn(shape_kv, device=dev, dtype=torch.bfloat16, generator=g)
+    v = torch.randn(shape_kv, device=dev, dtype=torch.bfloat16, generator=g)
+    out = torch.empty_like(q)
+    pos = {"t_pos": torch.full((cfg.B, cfg.T), cfg.frame_t, dtype=torch.long, device=dev)}
+
+    def forward_layers():
+        for li in range(N_LAYERS):
+            layer = cache.layers[li]
+            ops.append_attend(q[li], k[li], v[li], layer.kv, layer.written.view(torch.uint8), pos["t_pos"],
+                              cfg.T, 1, True, 0.0, out=out[li])
+
+    def attention_only():
+        for li in range(N_LAYERS):
+            layer = cache.layers[li]
+            ops.frame_attn(q[li], layer.kv, layer.written.view(torch.uint8), pos["t_pos"], cfg.T, 1, 0.0, out=out[li])
+
+    # warm-up outside graphs (allocates the workspace, sets function attributes)
+    forward_layers()
+    attention_only()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=dev)
+    graph_step, graph_attn = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        n0 = lib.we_b200_launch_count()
+        with torch.cuda.graph(graph_step, stream=side):
+            forward_layers()
+        launches_per_step = lib.we_b200_launch_count() - n0
+        with torch.cuda.graph(graph_attn, stream=side):
+            attention_only()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(max(args.warmup, 3)):
+        graph_step.replay()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph_step.replay()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+
+        # the dominant kernel alone (attention, no append), same caches, same stream
+        for _ in range(3):
+            graph_attn.replay()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        for _ in range(args.steps):
+            graph_attn.replay()
+        a1.record(stream)
+        torch.cuda.synchronize()
+        attn_us = a0.elapsed_time(a1) * 1e3 / (args.steps * N_LAYERS)
+    ops.check_status(dev)
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "us_per_layer_step": ms * 1e3 / (N_LAYERS * args.steps),
+                              "attn_us_per_launch": attn_us}))
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    # end to end through the public API: inputs from pinned host memory, output read back, every step
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    hout = torch.empty(shape_q, dtype=torch.bfloat16).pin_memory()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        for li in range(N_LAYERS):
+            y = cache.append_and_attend(dq[li], dk[li], dv[li], pos, li)
+            hout[li].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+        return float(hout[0, 0, 0, 0, 0])
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
+    d2h = hout.numel() * 2
+
+    # max over ranks
+    times = torch.tensor([ms, e2e_s * 1e3, attn_us], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, attn_us = (float(x) for x in times.tolist())
+
+    if rank == 0:
+        hbm_peak, tc_peak, peak_kind = measured_peaks()
+        total_layer_steps = world * N_LAYERS * args.steps
+        value = total_layer_steps / (ms * 1e-3)
+        us_per_layer_step = ms * 1e3 / (N_LAYERS * args.steps)
+        elem = 2
+        attn_bytes = cfg.B * (2 * cfg.Hkv * cfg.visible_keys() * cfg.Dh * elem + 2 * cfg.Hq * cfg.T * cfg.Dh * elem)
+        achieved = attn_bytes / (attn_us * 1e-6) / 1e9
+        cpu = None
+        if world == 1:   # reported baseline: rank 0 at N=1 only
+            cpu_med, cpu_times = cpu_layer_step_seconds(cfg, 40)
+            cpu = {"value": 1.0 / cpu_med, "unit": "layer-steps/s", "cores": host_threads(), "kind": "port",
+                   "sample": f"{len(cpu_times)} layer-steps of the cfg2 shape, median (numpy oracle)"}
+        line = {
+            "metric": "frame-attn layer-steps/s (append + attention)", "value": value, "unit": "layer-steps/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layer_steps_per_step": N_LAYERS, "sessions_per_gpu": 1,
+                       "l2": "inputs larger than L2 (855 MB of cache per step)"},
+            "us_per_layer_step": us_per_layer_step,
+            "tflops": cfg.flops() / (us_per_layer_step * 1e-6) / 1e12,
+            "sessions_frames_per_s": value / (N_LAYERS * 5),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "frame_attn_kernel<128,bf16>", "us_per_launch": attn_us,
+                         "algorithmic_bytes_per_launch": attn_bytes},
+            "cpu_baseline": cpu,
+            "e2e": {"value": total_layer_steps / (e2e_ms * 1e-3), "unit": "layer-steps/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches_per_step) * args.steps,
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--profile", action="store_true",
+                    help="device-timed legs only (skips the end-to-end and CPU-baseline legs): for runs under ncu")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -79,12 +79,24 @@ struct AttnParams {
   float* ws_ml;                  // [unit][split][2][128]
   int32_t* ws_cnt;               // [unit]
   int32_t* status;
-  float* debug;                  // optional dump of the first S tile (debug builds)
 };
 
 #ifdef WE_ATTN_DEBUG
-// Debug builds only: descriptor fields overridable at run time (0 = keep the default).
+// Debug builds only: descriptor fields overridable at run time (0 = keep the default), and a
+// per-CTA timeline (SM cycles since the CTA started) written to a caller-provided buffer.
 __constant__ uint32_t g_dbg[8];
+__device__ uint32_t* g_trace = nullptr;
+#define WE_TRACE(slot)                                                                             \
+  do {                                                                                             \
+    if (trace != nullptr) trace[(slot)] = static_cast<uint32_t>(clock64() - t_start);              \
+  } while (0)
+#define WE_TRACE_VAL(slot, val)                                                                    \
+  do {                                                                                             \
+    if (trace != nullptr) trace[(slot)] = static_cast<uint32_t>(val);                              \
+  } while (0)
+#else
+#define WE_TRACE(slot) do {} while (0)
+#define WE_TRACE_VAL(slot, val) do {} while (0)
 #endif
 
 template <bool BF16>
@@ -143,6 +155,20 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int b = blockIdx.z;
   const int kvh = h / (p.Hq / p.Hkv);
   const int q0 = qt * kBlockM;
+#ifdef WE_ATTN_DEBUG
+  const long long t_start = clock64();
+  uint32_t* trace = nullptr;
+  {
+    const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (g_trace != nullptr && cta < 64u) trace = g_trace + cta * 256u;
+    if (trace != nullptr && tid == 0) {
+      uint32_t smid;
+      asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+      trace[0] = static_cast<uint32_t>(global_timer_ns());
+      trace[230] = smid;
+    }
+  }
+#endif
 
   // ---------------------------------------------------------------- set-up
   if (tid == 0) *s_abort = 0;
@@ -184,6 +210,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (tid == 0) WE_TRACE(1);
   const uint32_t tmem_base = *s_tmem;
   const int64_t slot_base = s_slot[0];
   const bool hide = s_slot[1] != 0;
@@ -231,6 +258,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int t0 = static_cast<int>((static_cast<int64_t>(n_list) * split) / p.nsplit);
   const int t1 = static_cast<int>((static_cast<int64_t>(n_list) * (split + 1)) / p.nsplit);
   const int n = t1 - t0;
+  if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
   // ------------------------------------------------------------------ roles
   if (warp == 4) {
@@ -238,6 +266,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int i = 0; i < n; ++i) {
         const int st = i % kStages;
         if (i >= kStages) mbar_wait(&kv_empty[st], ((i / kStages) - 1) & 1, s_abort);
+        if (i < 32) WE_TRACE(192 + i);
         const int key0 = (s_list[t0 + i] >> 1) * kBlockN;
         const int v3[3] = {key0, kvh, b};
         const int c1 = v3[p.kv_perm[0]], c2 = v3[p.kv_perm[1]], c3 = v3[p.kv_perm[2]];
@@ -276,7 +305,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int st = i % kStages;
         if (i + 1 < n) issue_s(i + 1);
         mbar_wait(&p_ready[i & 1], (i >> 1) & 1, s_abort);
+        if (i < 24) WE_TRACE(144 + 2 * i);
         mbar_wait(&v_full[st], (i / kStages) & 1, s_abort);
+        if (i < 24) WE_TRACE(145 + 2 * i);
         tc_fence_after();
         // O += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16.
         const uint32_t d = tmem_base + kColO;
@@ -309,6 +340,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t s_addr = tmem_base + lane_base + (buf ? kColS1 : kColS0);
       const uint32_t p_addr = tmem_base + lane_base + (buf ? kColP1 : kColP0);
       mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
+      if (tid == 0 && i < 32) WE_TRACE(16 + 4 * i);
       tc_fence_after();
       uint32_t s[4][32];
       tmem_ld32(s_addr + 0, s[0]);
@@ -331,22 +363,18 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       }
-#ifdef WE_ATTN_DEBUG
-      if (p.debug != nullptr && i == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        for (int c = 0; c < 4; ++c)
-          for (int j = 0; j < 32; ++j) p.debug[row * 128 + c * 32 + j] = __uint_as_float(s[c][j]);
-      }
-#endif
       float mx = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(s[c][j]));
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      if (tid == 0 && i < 32) WE_TRACE(17 + 4 * i);
       if (i > 0) {
         mbar_wait(o_ready, (i - 1) & 1, s_abort);  // O holds tiles < i and no MMA is writing it
         tc_fence_after();
       }
+      if (tid == 0 && i < 32) WE_TRACE(18 + 4 * i);
       const bool need = (m_new - m_run) > kRescaleThreshold;  // first tile: inf > threshold
       if (__any_sync(0xffffffffu, need)) {
         const float alpha = exp2f(m_run - m_new);             // first tile: exp2(-inf) = 0
@@ -381,6 +409,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_ready[buf]);
+      if (tid == 0 && i < 32) WE_TRACE(19 + 4 * i);
     }
 
     // ------------------------------------------------------------ epilogue
@@ -388,6 +417,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(o_ready, (n - 1) & 1, s_abort);
       tc_fence_after();
     }
+    if (tid == 0) WE_TRACE(224);
     const int unit = (b * p.Hq + h) * p.n_qtiles + qt;
     if (p.nsplit == 1) {
       const float inv = 1.0f / l_run;
@@ -432,8 +462,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       __stcg(wml + kBlockM + row, l_run);
       __threadfence();
       named_bar_sync(1, 128);
+      if (tid == 0) WE_TRACE(225);
       if (tid == 0) *s_ticket = static_cast<uint32_t>(atomicAdd(p.ws_cnt + unit, 1));
       named_bar_sync(1, 128);
+      if (tid == 0) { WE_TRACE(226); WE_TRACE_VAL(229, *s_ticket); }
       if (*s_ticket == static_cast<uint32_t>(p.nsplit - 1)) {
         // Last split to arrive merges all of them, always in split order (deterministic).
         __threadfence();
@@ -474,6 +506,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         if (tid == 0) p.ws_cnt[unit] = 0;  // leave the counter ready for the next launch
+        if (tid == 0) WE_TRACE(227);
       }
     }
   }
@@ -481,6 +514,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // --------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
+  if (tid == 0) WE_TRACE(228);
   if (*s_abort != 0) {
     if (tid == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_WAIT_EXPIRED);
     __nanosleep(1000000);  // let copies and MMAs that are still in flight land before the CTA goes away
@@ -646,12 +680,6 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   p.ws_ml = reinterpret_cast<float*>(ws + sp.cnt_bytes);
   p.ws_o = reinterpret_cast<float*>(ws + sp.cnt_bytes + sp.ml_bytes);
   p.status = status;
-  p.debug = nullptr;
-#ifdef WE_ATTN_DEBUG
-  // debug builds: the caller passes a workspace with 64 KiB of extra room at its end
-  if (workspace != nullptr && workspace_bytes >= need + 65536) p.debug = reinterpret_cast<float*>(ws + workspace_bytes - 65536);
-#endif
-
   CUtensorMap tq, tk, tv;
   const int64_t kvs[3] = {g->kv_batch_stride, C * g->Dh, static_cast<int64_t>(g->Dh)};
   if ((rc = make_map(&tq, q, g->dtype, g->T, Hq, g->B, g->Dh, qs, p.q_perm)) != WE_B200_OK) return rc;
@@ -675,6 +703,10 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
 extern "C" __attribute__((visibility("default"))) int we_b200_debug_set(int idx, uint32_t value) {
   if (idx < 0 || idx >= 8) return -1;
   return static_cast<int>(cudaMemcpyToSymbol(we::g_dbg, &value, sizeof(value), idx * sizeof(uint32_t)));
+}
+// Buffer of 64 x 256 uint32 for the per-CTA timeline (null switches tracing off).
+extern "C" __attribute__((visibility("default"))) int we_b200_debug_trace(uint32_t* buf) {
+  return static_cast<int>(cudaMemcpyToSymbol(we::g_trace, &buf, sizeof(buf)));
 }
 #endif
 
