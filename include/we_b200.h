@@ -67,7 +67,9 @@ enum {
   WE_B200_E_DTYPE = -4,       /* dtype / head_dim unsupported by this kernel     */
   WE_B200_E_WORKSPACE = -5,   /* workspace missing or too small                  */
   WE_B200_E_DRIVER = -6,      /* tensor-map encoder unavailable / encode failed  */
-  WE_B200_E_LIMIT = -7        /* a size exceeds a documented maximum             */
+  WE_B200_E_LIMIT = -7,       /* a size exceeds a documented maximum             */
+  WE_B200_E_STATIC_SCRATCH = -8 /* shape needs more scratch than the built-in array of
+                                   we_b200_frame_attn_static holds (12 MiB)       */
 };
 
 /* Device status codes written to *status by the attention kernel. */
@@ -169,6 +171,28 @@ WE_B200_API int we_b200_append_attend(const void* q, const int64_t* q_strides_ho
                           int is_frozen, float scale,
                           void* workspace, size_t workspace_bytes,
                           int32_t* status, void* stream);
+
+/*
+ * we_b200_frame_attn for callers that cannot allocate device memory.  (No counterpart in the reference,
+ * which lets PyTorch allocate whatever its kernels need.)  Meant for hosts that are forbidden to call
+ * the device allocator while running -- a real-time frame loop that gave all GPU memory to its own arena
+ * up front, a plug-in that may only use the buffers it is handed -- and therefore cannot supply the
+ * split-KV workspace.  Same arguments and results as we_b200_frame_attn minus the workspace: the scratch
+ * lives in a 12 MiB array inside the library image (held by every GPU that loads the library until the
+ * process ends).  Shapes whose split-KV plan needs more return WE_B200_E_STATIC_SCRATCH and launch
+ * nothing; we_b200_attn_workspace_bytes tells the need in advance.  The call itself performs no
+ * cudaMalloc / cudaFree and calls no allocating routine; inputs, output and status word are still the
+ * caller's buffers.  The first call on each device looks up the array's device address (that device
+ * must be current) -- make that first call before any stream capture begins.  All calls share the one
+ * array: it keeps the previous call's contents (the entry point re-zeroes the small part that must
+ * start at zero, on `stream`), and two calls that overlap on the GPU -- different streams, or several
+ * host threads -- race on it.  Keep calls to this entry point ordered on one stream per device.
+ */
+WE_B200_API int we_b200_frame_attn_static(const void* q, const int64_t* q_strides_host,
+                              void* out, const int64_t* out_strides_host, int32_t Hq,
+                              const void* kv, const uint8_t* written, const int64_t* frame_t,
+                              const we_b200_cache_geom* geom_host, float scale,
+                              int32_t* status, void* stream);
 
 /* Number of kernels the previous three entry points have launched in this
  * process (diagnostic counter for benchmarks; relaxed atomics). */

@@ -24,6 +24,7 @@ EXPORTS = (
     "we_b200_attn_workspace_bytes",
     "we_b200_frame_attn",
     "we_b200_append_attend",
+    "we_b200_frame_attn_static",
     "we_b200_launch_count",
 )
 
@@ -95,6 +96,11 @@ def load() -> ctypes.CDLL:
         c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64),
         c_void_p, c_void_p, c_void_p, c_void_p, POINTER(CacheGeom), c_int, c_float,
         c_void_p, c_size_t, c_void_p, c_void_p]
+
+    lib.we_b200_frame_attn_static.restype = c_int
+    lib.we_b200_frame_attn_static.argtypes = [
+        c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_int32,
+        c_void_p, c_void_p, c_void_p, POINTER(CacheGeom), c_float, c_void_p, c_void_p]
 
     got = lib.we_b200_abi_version()
     if got != ABI_VERSION:

@@ -18,6 +18,9 @@ extern "C" const char* we_b200_strerror(int code) {
     case WE_B200_E_WORKSPACE: return "workspace missing or too small";
     case WE_B200_E_DRIVER: return "tensor-map encoder unavailable or rejected the layout";
     case WE_B200_E_LIMIT: return "a size exceeds a documented maximum";
+    case WE_B200_E_STATIC_SCRATCH:
+      return "this shape needs more split-KV scratch than the 12 MiB built into we_b200_frame_attn_static; "
+             "use we_b200_frame_attn with a caller-provided workspace";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

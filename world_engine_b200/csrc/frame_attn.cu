@@ -35,6 +35,8 @@
 #include <cuda_fp16.h>
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -722,4 +724,54 @@ extern "C" int we_b200_frame_attn(const void* q, const int64_t* q_strides_host, 
                                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
                                workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------- entry point that allocates nothing
+// Some hosts of this library are not allowed to obtain device memory at all once they are running: a
+// real-time frame loop that handed the whole GPU to its own arena at start-up and treats every later
+// driver allocation as a fault (it may stall the device or fail when memory is fragmented), or a plug-in
+// host that may only touch the buffers it is handed.  Such callers cannot provide the split-KV
+// workspace.  For them the same attention kernel is offered with its scratch in a fixed array that is
+// part of the loaded library image: every GPU that loads the library holds these bytes until the
+// process exits, which is why the array is kept modest.
+namespace we {
+constexpr size_t kStaticScratchBytes = 12u << 20;  // 12 MiB: covers every split-KV plan on a 148-SM part at Dh <= 128
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+}  // namespace we
+
+extern "C" int we_b200_frame_attn_static(const void* q, const int64_t* q_strides_host, void* out,
+                                         const int64_t* out_strides_host, int32_t Hq, const void* kv,
+                                         const uint8_t* written, const int64_t* frame_t,
+                                         const we_b200_cache_geom* geom_host, float scale, int32_t* status,
+                                         void* stream) {
+  // In host code `g_static_scratch` is only a handle for the symbol, not a device address: the address
+  // on the current device has to be asked for, once per device, with that device current.
+  static std::mutex mu;
+  static void* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return WE_B200_E_LIMIT;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (scratch_of_device[dev] == nullptr) {
+      void* ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, we::g_static_scratch);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      scratch_of_device[dev] = ptr;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  if (geom_host == nullptr) return WE_B200_E_NULL;
+  if (geom_host->B < 1 || Hq < 1 || geom_host->T < 1 || geom_host->Dh < 1 || geom_host->L < 1) return WE_B200_E_SHAPE;
+  const we::SplitPlan sp = we::plan_splits(geom_host->B, Hq, geom_host->T, geom_host->Dh, geom_host->L);
+  if (sp.o_bytes + sp.ml_bytes + sp.cnt_bytes > we::kStaticScratchBytes) return WE_B200_E_STATIC_SCRATCH;
+  // The array keeps whatever the previous call left.  Only the arrival counters must start at zero (the
+  // kernel restores them, but a call that was cut short may not have): clear them on the caller's stream.
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  e = cudaMemsetAsync(scratch, 0, sp.cnt_bytes, s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
+                               scratch, we::kStaticScratchBytes, status, s);
 }

@@ -137,6 +137,27 @@ def frame_attn(q: torch.Tensor, kv: torch.Tensor, written: torch.Tensor, frame_t
     return out
 
 
+def frame_attn_no_alloc(q: torch.Tensor, out: torch.Tensor, status: torch.Tensor, kv: torch.Tensor,
+                        written: torch.Tensor, frame_t: torch.Tensor, tokens_per_frame: int, dilation: int,
+                        scale: float = 0.0, frame_t_stride: int = 0) -> torch.Tensor:
+    """`frame_attn` for hosts that must not allocate device memory while running (an engine that gave
+    the whole GPU to its own arena, a plug-in limited to the buffers it receives): binds
+    we_b200_frame_attn_static, whose split-KV scratch is a fixed 12 MiB array inside the library.
+    Nothing is allocated here either, so `out` (q's shape) and `status` (one int32) are the caller's.
+    Raises WeB200Error (code -8) for shapes that need more scratch.  Calls share that one array:
+    keep them on one stream per device, and make the first call on a device outside stream capture."""
+    _require_cuda(q, out, status, kv, written, frame_t)
+    g = make_geom(kv, written, tokens_per_frame, dilation, frame_t_stride)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        rc = lib.we_b200_frame_attn_static(
+            q.data_ptr(), _strides3(q), out.data_ptr(), _strides3(out), q.size(1),
+            kv.data_ptr(), written.data_ptr(), frame_t.data_ptr(), ctypes.byref(g), float(scale),
+            status.data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "we_b200_frame_attn_static")
+    return out
+
+
 def append_attend(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv: torch.Tensor,
                   written: torch.Tensor, frame_t: torch.Tensor, tokens_per_frame: int, dilation: int,
                   is_frozen: bool, scale: float = 0.0, out: Optional[torch.Tensor] = None,
