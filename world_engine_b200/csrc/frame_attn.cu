@@ -11,19 +11,28 @@
 // only "which tiles are listed"; nothing is gathered or copied.
 //
 // One CTA = 128 queries of one (batch row, head) x one split of the tile
-// list.  Warp roles (192 threads):
-//   warps 0-3  softmax: thread r owns query row r (TMEM lane r); online
-//              softmax in fp32 with exp2 and a lazily updated row maximum;
-//              writes P (bf16/f16) back to tensor memory; rescales O only
-//              when a row maximum grew by more than 2^8.
-//   warp 4     producer: TMA loads of Q once and of K / V tiles through a
-//              ring of shared-memory stages guarded by mbarriers.
-//   warp 5     MMA issuer: tcgen05.mma S = Q K^T (both operands in shared
-//              memory, K-major, 128-byte swizzle) into one of two S buffers in
-//              tensor memory, and O += P V with P read from tensor memory
-//              and V from shared memory (MN-major).  Owns the TMEM allocation.
-// S is double-buffered so the tensor pipe computes S(i+1) while the softmax
-// warps work on S(i).
+// list.  Warp roles (384 threads):
+//   warps 0-3   softmax stream A: tiles 0, 2, 4, ... of the CTA's share
+//   warps 4-7   softmax stream B: tiles 1, 3, 5, ...
+//               Thread r of either group owns query row r (TMEM lane r), so
+//               row max and row sum are in-thread reductions.  Each stream
+//               keeps its own running maximum, row sum and O accumulator, so
+//               the two never synchronise; they are merged once at the end.
+//               exp2 with the scale folded in; the running maximum is raised
+//               (and O rescaled in tensor memory) only when it grew by more
+//               than 2^8; P (bf16/f16) overwrites the first half of its S.
+//   warp 8      producer: builds the visible-tile list on its own (no
+//               block-wide step), TMA-loads Q once and then the K tiles
+//               through a ring of shared-memory stages.
+//   warp 10     V producer: the V tiles through a ring of their own.
+//   warp 9      MMA issuer and TMEM owner: tcgen05.mma S = Q K^T (both
+//               operands in shared memory, K-major, 128-byte swizzle) and
+//               O += P V (P from tensor memory, V from shared memory as an
+//               MN-major operand), in the order S0 S1 PV0 S2 PV1 S3 ... so
+//               the tensor pipe works on one stream while the softmax warps
+//               work on the other.
+//   warp 11     idle (rounds the block up to three warpgroups).
+// Tensor memory (512 columns): S_A, S_B, O_A, O_B, 128 columns each.
 //
 // Split-KV: when (batch x heads x query tiles) cannot fill the SMs, the tile
 // list is split over several CTAs.  Each writes its un-normalised O, row
@@ -45,10 +54,12 @@ namespace we {
 constexpr int kBlockM = 128;    // queries per CTA (= TMEM lanes)
 constexpr int kBlockN = 128;    // keys per tile
 constexpr int kMaxTiles = 1024; // capacity limit: 131072 tokens per (row, head)
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 384;
+constexpr int kSoftmaxThreads = 256;
 constexpr int kMaxSplits = 32;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256, kColP0 = 384, kColP1 = 448;
+constexpr uint32_t kColS = 0;    // + 128 * stream
+constexpr uint32_t kColO = 256;  // + 128 * stream
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int DH>
@@ -56,10 +67,19 @@ struct AttnCfg {
   static constexpr int kChunks = DH / 64;                 // 128-byte column chunks per row
   static constexpr int kChunkBytes = kBlockN * 128;       // one chunk of a 128-row tile
   static constexpr int kTileBytes = kChunks * kChunkBytes;
-  static constexpr int kStages = DH == 128 ? 2 : 4;       // K/V stages; keeps smem > half an SM
-  static constexpr int kSmemTiles = kTileBytes * (1 + 2 * kStages);
-  static constexpr int kSmemAux = 64 * 8 + kMaxTiles * 4 + kMaxTiles * 2 + 64;
+  static constexpr int kStagesK = DH == 128 ? 3 : 4;      // stage counts also keep smem above half an SM,
+  static constexpr int kStagesV = DH == 128 ? 2 : 4;      // so two CTAs never share an SM's tensor memory
+  static constexpr int kSmemTiles = kTileBytes * (1 + kStagesK + kStagesV);
+  static constexpr int kSmemAux = 64 * 8 + kMaxTiles * 2 + 64 + 4 * kBlockM * 4 + kMaxTiles;
   static constexpr int kSmemBytes = kSmemTiles + kSmemAux + 1024;  // + slack for 1024-byte alignment
+  // Exchange buffers of the epilogue, laid over the (then idle) rings: the CTA's partial O tile
+  // [128][DH + 4] fp32 over the K ring (row maximum and row sum in the first two pad columns), and the
+  // rows received from the other splits over the V ring.
+  static constexpr int kPartRow = DH + 4;
+  static constexpr int kPartFloats = kBlockM * kPartRow;
+  static_assert(kPartFloats * 4 <= kStagesK * kTileBytes, "the partial tile must fit in the K ring");
+  static_assert(kPartFloats * 4 <= kStagesV * kTileBytes + kPartRow * 4 * 16,
+                "the rows received from up to 7 peers (at most 7/8 of a tile) must fit in the V ring");
 };
 
 struct AttnParams {
@@ -73,6 +93,7 @@ struct AttnParams {
   int32_t C;                     // L + T
   int32_t T, Hq, Hkv, dilation;
   int32_t ntiles;                // ceil(C / 128)
+  int32_t ring_frames;           // L / T
   int32_t nsplit, n_qtiles;
   int32_t q_perm[3];             // which of (t, h, b) feeds tensor-map coordinate 1, 2, 3
   int32_t kv_perm[3];
@@ -81,16 +102,20 @@ struct AttnParams {
   float* ws_ml;                  // [unit][split][2][128]
   int32_t* ws_cnt;               // [unit]
   int32_t* status;
+  int32_t cluster_merge;         // 1: the splits of a query tile form a thread-block cluster and merge through DSMEM
 };
 
 #ifdef WE_ATTN_DEBUG
-// Debug builds only: descriptor fields overridable at run time (0 = keep the default), and a
-// per-CTA timeline (SM cycles since the CTA started) written to a caller-provided buffer.
-__constant__ uint32_t g_dbg[8];
+// Debug builds only: a per-CTA timeline (SM cycles since the CTA started) written to a caller-provided buffer.
 __device__ uint32_t* g_trace = nullptr;
+__device__ __forceinline__ long long trace_clock() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+  return t;
+}
 #define WE_TRACE(slot)                                                                             \
   do {                                                                                             \
-    if (trace != nullptr) trace[(slot)] = static_cast<uint32_t>(clock64() - t_start);              \
+    if (trace != nullptr) trace[(slot)] = static_cast<uint32_t>(trace_clock() - t_start);          \
   } while (0)
 #define WE_TRACE_VAL(slot, val)                                                                    \
   do {                                                                                             \
@@ -116,12 +141,95 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+// Asynchronous bulk copy from this CTA's shared memory into a peer CTA's shared memory; completion is
+// signalled as transaction bytes on the peer's mbarrier.  All addresses and the size are 16-byte multiples.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
+                                                  uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          dst_cluster_addr),
+      "r"(src_cta_addr), "r"(bytes), "r"(bar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// Is token `key` visible to this call?  (written, not in the hidden slot, inside the buffer.)
+__device__ __forceinline__ bool token_visible(const uint8_t* wr, int key, int C, bool hide, int64_t slot_base, int T) {
+  if (key >= C) return false;
+  if (hide && key >= slot_base && key < slot_base + T) return false;
+  return wr[key] != 0;
+}
+
+// Visibility bits of 32 consecutive tokens starting at key0 (partial tiles only; rare path).
+__device__ __noinline__ uint32_t chunk_visibility(const uint8_t* wr, int key0, int C, bool hide, int64_t slot_base,
+                                                  int T) {
+  uint32_t bits = 0;
+  for (int j = 0; j < 32; ++j) bits |= token_visible(wr, key0 + j, C, hide, slot_base, T) ? (1u << j) : 0u;
+  return bits;
+}
+
+// 16 bytes of `written` starting at token 16*v (zeros past the end of the buffer).
+__device__ __forceinline__ uint4 load_written16(const uint8_t* wr, int v, int C) {
+  uint4 w = make_uint4(0u, 0u, 0u, 0u);
+  if (v * 16 + 16 <= C) {
+    w = *reinterpret_cast<const uint4*>(wr + v * 16);
+  } else if (v * 16 < C) {
+    uint32_t ww[4] = {0u, 0u, 0u, 0u};
+#pragma unroll 1
+    for (int key = v * 16; key < C; ++key) {
+      const uint32_t bit = (wr[key] != 0 ? 1u : 0u) << ((key & 3) * 8);
+      const int word = (key & 15) >> 2;
+      ww[0] |= word == 0 ? bit : 0u;
+      ww[1] |= word == 1 ? bit : 0u;
+      ww[2] |= word == 2 ? bit : 0u;
+      ww[3] |= word == 3 ? bit : 0u;
+    }
+    w = make_uint4(ww[0], ww[1], ww[2], ww[3]);
+  }
+  return w;
+}
+
 template <int DH, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   using Cfg = AttnCfg<DH>;
-  constexpr int kStages = Cfg::kStages;
+  constexpr int kStagesK = Cfg::kStagesK;
+  constexpr int kStagesV = Cfg::kStagesV;
   constexpr uint32_t kInFmt = BF16 ? 1u : 0u;
   constexpr uint32_t kIdescS = umma_idesc(kInFmt, 0u, kBlockM, kBlockN);
   constexpr uint32_t kIdescPV = umma_idesc(kInFmt, 1u, kBlockM, DH);
@@ -130,35 +238,39 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + Cfg::kTileBytes;
-  uint8_t* sV = sK + kStages * Cfg::kTileBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kStages * Cfg::kTileBytes);
+  uint8_t* sV = sK + kStagesK * Cfg::kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kStagesV * Cfg::kTileBytes);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;              // [kStages]
-  uint64_t* v_full = bars + 1 + kStages;    // [kStages]
-  uint64_t* kv_empty = bars + 1 + 2 * kStages;  // [kStages]
-  uint64_t* s_ready = bars + 1 + 3 * kStages;   // [2]
-  uint64_t* p_ready = s_ready + 2;              // [2]
-  uint64_t* o_ready = p_ready + 2;              // [1]
-  uint32_t* s_cnt = reinterpret_cast<uint32_t*>(bars + 64);       // [kMaxTiles] visible keys per tile
-  uint16_t* s_list = reinterpret_cast<uint16_t*>(s_cnt + kMaxTiles);  // [kMaxTiles] (tile << 1) | partial
+  uint64_t* recv_bar = bars + 1;  // incoming partial rows of the split merge
+  uint64_t* s_ready = bars + 2;   // [2] per stream
+  uint64_t* p_ready = bars + 4;   // [2]
+  uint64_t* o_final = bars + 6;   // [2]
+  uint64_t* k_full = bars + 8;                  // [kStagesK]
+  uint64_t* k_empty = k_full + kStagesK;        // [kStagesK]
+  uint64_t* v_full = k_empty + kStagesK;        // [kStagesV]
+  uint64_t* v_empty = v_full + kStagesV;        // [kStagesV]
+  uint16_t* s_list = reinterpret_cast<uint16_t*>(bars + 64);          // [kMaxTiles] (tile << 1) | partial
   uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_list + kMaxTiles);
   uint32_t* s_tmem = s_misc + 0;
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_misc + 1);
-  uint32_t* s_nlist = s_misc + 2;
+  volatile uint32_t* s_nlist = s_misc + 2;
   uint32_t* s_ticket = s_misc + 3;
-  int64_t* s_slot = reinterpret_cast<int64_t*>(s_misc + 4);       // [0] base, [1] hide flag
+  volatile int64_t* s_slot = reinterpret_cast<volatile int64_t*>(s_misc + 4);  // [0] base, [1] hide flag
+  float* s_ml = reinterpret_cast<float*>(s_misc + 16);                // [stream][m, l][128]
+  uint8_t* s_cnt = reinterpret_cast<uint8_t*>(s_ml + 4 * kBlockM);    // [kMaxTiles] visible keys per tile (128 -> 128)
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int qt = blockIdx.x % p.n_qtiles;
-  const int split = blockIdx.x / p.n_qtiles;
+  const int split = blockIdx.x % p.nsplit;   // consecutive blocks = the splits of one query tile (one cluster)
+  const int qt = blockIdx.x / p.nsplit;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int kvh = h / (p.Hq / p.Hkv);
   const int q0 = qt * kBlockM;
+  const uint8_t* wr = p.written + static_cast<int64_t>(b) * p.written_batch_stride;
 #ifdef WE_ATTN_DEBUG
-  const long long t_start = clock64();
+  const long long t_start = trace_clock();
   uint32_t* trace = nullptr;
   {
     const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
@@ -173,22 +285,29 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #endif
 
   // ---------------------------------------------------------------- set-up
+  // Issue the only global loads of the prologue right away; they are consumed after the set-up barrier.
+  const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
+  const uint4 w_first = load_written16(wr, tid, p.C);
   if (tid == 0) *s_abort = 0;
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     prefetch_tensormap(&tm_q);
     prefetch_tensormap(&tm_k);
     prefetch_tensormap(&tm_v);
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&v_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    mbar_init(recv_bar, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_ready[s], 1);
+      mbar_init(&p_ready[s], 128);
+      mbar_init(&o_final[s], 1);
     }
-    mbar_init(&s_ready[0], 1);
-    mbar_init(&s_ready[1], 1);
-    mbar_init(&p_ready[0], 128);
-    mbar_init(&p_ready[1], 128);
-    mbar_init(o_ready, 1);
+    for (int s = 0; s < kStagesK; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < kStagesV; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
     fence_mbar_init();
     fence_proxy_async_smem();
     // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
@@ -198,275 +317,353 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, v3[p.q_perm[0]], v3[p.q_perm[1]],
                   v3[p.q_perm[2]]);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
   }
-  if (tid == 32) {
-    const int64_t t = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
-    const SlotInfo s = slot_of(t, p.L, p.T, p.dilation);
-    s_slot[0] = s.base;
-    s_slot[1] = s.write_step;
-  }
-  for (int j = tid; j < p.ntiles; j += kAttnThreads) s_cnt[j] = 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   if (tid == 0) WE_TRACE(1);
   const uint32_t tmem_base = *s_tmem;
-  const int64_t slot_base = s_slot[0];
-  const bool hide = s_slot[1] != 0;
-  const uint8_t* wr = p.written + static_cast<int64_t>(b) * p.written_batch_stride;
 
-  // ------------------------------------------------ visible-tile list (per CTA)
-  // Each thread inspects 16 tokens at a time and adds its visible count to the tile's counter.
+  // ------------------------------------------------------ visible-tile list
+  // All threads: 16 tokens each, eight lanes make one 128-key tile; the per-tile counts go to shared
+  // memory and the producer warp compacts them.  (The global loads were issued before the set-up barrier.)
   {
+    int slot_base, hide_i;
+    if (static_cast<uint64_t>(ft) < 0x7FFFFFFFull) {
+      // same arithmetic as slot_of(), in 32 bits
+      const uint32_t t = static_cast<uint32_t>(ft), d = static_cast<uint32_t>(p.dilation);
+      const uint32_t buckets = static_cast<uint32_t>(p.ring_frames) / d;
+      slot_base = static_cast<int>((((t + d - 1u) / d) % buckets) * static_cast<uint32_t>(p.T));
+      hide_i = (t % d) == 0u;
+    } else {
+      const SlotInfo si = slot_of(ft, p.L, p.T, p.dilation);
+      slot_base = static_cast<int>(si.base);
+      hide_i = si.write_step;
+    }
+    if (tid == 0) {
+      s_slot[0] = slot_base;
+      s_slot[1] = hide_i;
+    }
+    const int hid_lo = hide_i ? slot_base : 0, hid_hi = hide_i ? slot_base + p.T : 0;  // hidden token range
     const int nvec = (p.C + 15) >> 4;
-    for (int v = tid; v < nvec; v += kAttnThreads) {
-      const int k0 = v << 4;
-      int cnt = 0;
-      if (k0 + 16 <= p.C) {
-        const uint4 w = *reinterpret_cast<const uint4*>(wr + k0);
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int key = k0 + j;
-          const bool in_slot = hide && key >= slot_base && key < slot_base + p.T;
-          cnt += (((ww[j >> 2] >> ((j & 3) * 8)) & 0xFFu) != 0u && !in_slot) ? 1 : 0;
-        }
-      } else {
-        for (int key = k0; key < p.C; ++key) {
-          const bool in_slot = hide && key >= slot_base && key < slot_base + p.T;
-          cnt += (wr[key] != 0 && !in_slot) ? 1 : 0;
+    const int nvec_pad = (nvec + 31) & ~31;  // whole warps take part in the shuffles
+#pragma unroll 1
+    for (int v = tid; v < nvec_pad; v += kAttnThreads) {
+      uint4 w = w_first;
+      if (v != tid) w = load_written16(wr, v, p.C);
+      const int k0 = v * 16;
+      // one bit per non-zero byte
+      const uint32_t nz0 = __vcmpne4(w.x, 0u) & 0x01010101u, nz1 = __vcmpne4(w.y, 0u) & 0x01010101u;
+      const uint32_t nz2 = __vcmpne4(w.z, 0u) & 0x01010101u, nz3 = __vcmpne4(w.w, 0u) & 0x01010101u;
+      int cnt = __popc(nz0) + __popc(nz1) + __popc(nz2) + __popc(nz3);
+      const int lo = max(k0, hid_lo), hi = min(k0 + 16, hid_hi);
+      if (lo < hi) {
+        if (lo == k0 && hi == k0 + 16) {
+          cnt = 0;                                   // the whole vector lies in the hidden slot
+        } else {
+#pragma unroll 1
+          for (int key = lo; key < hi; ++key) cnt -= (key < p.C && wr[key] != 0) ? 1 : 0;
         }
       }
-      if (cnt) atomicAdd(&s_cnt[k0 >> 7], static_cast<uint32_t>(cnt));
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
+      if ((lane & 7) == 0 && (v >> 3) < p.ntiles) s_cnt[v >> 3] = static_cast<uint8_t>(cnt);
     }
   }
   __syncthreads();
-  if (warp == 0) {
-    int n = 0;
+  int n_list = 0;
+  if (warp == 8) {
+#pragma unroll 1
     for (int base = 0; base < p.ntiles; base += 32) {
       const int j = base + lane;
-      const uint32_t c = j < p.ntiles ? s_cnt[j] : 0u;
-      const unsigned m = __ballot_sync(0xffffffffu, c != 0u);
-      if (c != 0u) s_list[n + __popc(m & ((1u << lane) - 1u))] = static_cast<uint16_t>((j << 1) | (c != kBlockN ? 1 : 0));
-      n += __popc(m);
+      const int c = j < p.ntiles ? s_cnt[j] : 0;
+      const unsigned m = __ballot_sync(0xffffffffu, c != 0);
+      if (c != 0) s_list[n_list + __popc(m & ((1u << lane) - 1u))] = static_cast<uint16_t>((j << 1) | (c != kBlockN ? 1 : 0));
+      n_list += __popc(m);
     }
-    if (lane == 0) *s_nlist = n;
+    if (lane == 0) *s_nlist = static_cast<uint32_t>(n_list);
+    __threadfence_block();
+    named_bar_arrive(2, kAttnThreads);   // the other warps sleep on this barrier instead of polling
+  } else {
+    named_bar_sync(2, kAttnThreads);
+    n_list = static_cast<int>(*s_nlist);
   }
-  __syncthreads();
-  const int n_list = static_cast<int>(*s_nlist);
   const int t0 = static_cast<int>((static_cast<int64_t>(n_list) * split) / p.nsplit);
   const int t1 = static_cast<int>((static_cast<int64_t>(n_list) * (split + 1)) / p.nsplit);
   const int n = t1 - t0;
   if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
   // ------------------------------------------------------------------ roles
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
+      // K ring: K(i) is issued as soon as S(i - kStagesK) has consumed its stage.
       for (int i = 0; i < n; ++i) {
-        const int st = i % kStages;
-        if (i >= kStages) mbar_wait(&kv_empty[st], ((i / kStages) - 1) & 1, s_abort);
-        if (i < 32) WE_TRACE(192 + i);
+        const int sk = i % kStagesK;
         const int key0 = (s_list[t0 + i] >> 1) * kBlockN;
         const int v3[3] = {key0, kvh, b};
-        const int c1 = v3[p.kv_perm[0]], c2 = v3[p.kv_perm[1]], c3 = v3[p.kv_perm[2]];
-        mbar_arrive_expect_tx(&k_full[st], Cfg::kTileBytes);
+        if (i >= kStagesK) mbar_wait(&k_empty[sk], ((i / kStagesK) - 1) & 1, s_abort);
+        if (i < 32) WE_TRACE(192 + i);
+        mbar_arrive_expect_tx(&k_full[sk], Cfg::kTileBytes);
         for (int ch = 0; ch < Cfg::kChunks; ++ch)
-          tma_load_4d(sK + st * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_k, &k_full[st], ch * 64, c1, c2, c3);
-        mbar_arrive_expect_tx(&v_full[st], Cfg::kTileBytes);
-        for (int ch = 0; ch < Cfg::kChunks; ++ch)
-          tma_load_4d(sV + st * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_v, &v_full[st], ch * 64, c1, c2, c3);
+          tma_load_4d(sK + sk * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_k, &k_full[sk], ch * 64,
+                      v3[p.kv_perm[0]], v3[p.kv_perm[1]], v3[p.kv_perm[2]]);
       }
       if (n == 0) mbar_wait(q_full, 0, s_abort);  // nobody else consumes Q: let the copy land before exit
     }
-  } else if (warp == 5) {
+    __syncwarp();
+  } else if (warp == 10) {
+    if (lane == 0) {
+      // V ring, on its own thread so that a full V ring never holds back a K load.
+      for (int i = 0; i < n; ++i) {
+        const int sv = i % kStagesV;
+        const int key0 = (s_list[t0 + i] >> 1) * kBlockN;
+        const int v3[3] = {key0, kvh, b};
+        if (i >= kStagesV) mbar_wait(&v_empty[sv], ((i / kStagesV) - 1) & 1, s_abort);
+        mbar_arrive_expect_tx(&v_full[sv], Cfg::kTileBytes);
+        for (int ch = 0; ch < Cfg::kChunks; ++ch)
+          tma_load_4d(sV + sv * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_v, &v_full[sv], ch * 64,
+                      v3[p.kv_perm[0]], v3[p.kv_perm[1]], v3[p.kv_perm[2]]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
     if (lane == 0 && n > 0) {
       const uint32_t q_addr = smem_u32(sQ);
       const uint32_t k_addr = smem_u32(sK);
       const uint32_t v_addr = smem_u32(sV);
       mbar_wait(q_full, 0, s_abort);
-      // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16.
+      // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; goes to stream i & 1.
       auto issue_s = [&](int i) {
-        const int st = i % kStages;
-        mbar_wait(&k_full[st], (i / kStages) & 1, s_abort);
+        const int sk = i % kStagesK;
+        mbar_wait(&k_full[sk], (i / kStagesK) & 1, s_abort);
         tc_fence_after();
-        const uint32_t d = tmem_base + ((i & 1) ? kColS1 : kColS0);
+        const uint32_t d = tmem_base + kColS + 128u * (i & 1);
 #pragma unroll
         for (int kk = 0; kk < DH / 16; ++kk) {
           const uint32_t off = (kk >> 2) * Cfg::kChunkBytes + (kk & 3) * 32;
           const uint64_t a = umma_desc_sw128(q_addr + off, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(k_addr + st * Cfg::kTileBytes + off, 16, 1024);
+          const uint64_t bd = umma_desc_sw128(k_addr + sk * Cfg::kTileBytes + off, 16, 1024);
           umma_ss(d, a, bd, kIdescS, kk > 0 ? 1u : 0u);
         }
+        tc_commit(&k_empty[sk]);
         tc_commit(&s_ready[i & 1]);
       };
       issue_s(0);
+      if (n > 1) issue_s(1);
       for (int i = 0; i < n; ++i) {
-        const int st = i % kStages;
-        if (i + 1 < n) issue_s(i + 1);
-        mbar_wait(&p_ready[i & 1], (i >> 1) & 1, s_abort);
+        const int st = i & 1;
+        const int sv = i % kStagesV;
+        mbar_wait(&p_ready[st], (i >> 1) & 1, s_abort);
         if (i < 24) WE_TRACE(144 + 2 * i);
-        mbar_wait(&v_full[st], (i / kStages) & 1, s_abort);
+        mbar_wait(&v_full[sv], (i / kStagesV) & 1, s_abort);
         if (i < 24) WE_TRACE(145 + 2 * i);
         tc_fence_after();
-        // O += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16.
-        const uint32_t d = tmem_base + kColO;
-        const uint32_t a_t = tmem_base + ((i & 1) ? kColP1 : kColP0);
-        uint32_t v_lbo = Cfg::kChunkBytes, v_sbo = 1024, v_kstep = 2048, idesc_pv = kIdescPV;
-#ifdef WE_ATTN_DEBUG
-        if (g_dbg[0]) v_lbo = g_dbg[0];
-        if (g_dbg[1]) v_sbo = g_dbg[1];
-        if (g_dbg[2]) v_kstep = g_dbg[2];
-        if (g_dbg[3]) idesc_pv = g_dbg[3];
-#endif
+        // O_st += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16.  P sits in the first 64
+        // columns of S_st (two bf16 per column).
+        const uint32_t d = tmem_base + kColO + 128u * st;
+        const uint32_t a_t = tmem_base + kColS + 128u * st;
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          const uint64_t bd = umma_desc_sw128(v_addr + st * Cfg::kTileBytes + kk * v_kstep, v_lbo, v_sbo);
-          umma_ts(d, a_t + kk * 8, bd, idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t bd = umma_desc_sw128(v_addr + sv * Cfg::kTileBytes + kk * 2048, Cfg::kChunkBytes, 1024);
+          umma_ts(d, a_t + kk * 8, bd, kIdescPV, (i >= 2 || kk > 0) ? 1u : 0u);
         }
-        tc_commit(&kv_empty[st]);
-        tc_commit(o_ready);
+        tc_commit(&v_empty[sv]);
+        if (i + 2 >= n) tc_commit(&o_final[st]);   // last tile of this stream
+        if (i + 2 < n) issue_s(i + 2);             // overwrites S_st / P(i): ordered behind PV(i) in the pipe
       }
     }
     __syncwarp();
-  } else {
+  } else if (warp < 8) {
     // ------------------------------------------------------- softmax warps
-    const int row = tid;  // query row within the tile == TMEM lane
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int st = warp >> 2;            // stream: 0 = even tiles, 1 = odd tiles
+    const int row = tid & 127;           // query row within the tile == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * st;
+    const uint32_t o_addr = tmem_base + lane_base + kColO + 128u * st;
+    const int64_t slot_base = s_slot[0];
+    const bool hide = s_slot[1] != 0;
     float m_run = -INFINITY;  // running row maximum, log2 domain, possibly stale by <= threshold
     float l_run = 0.f;
-    for (int i = 0; i < n; ++i) {
-      const int buf = i & 1;
-      const uint32_t s_addr = tmem_base + lane_base + (buf ? kColS1 : kColS0);
-      const uint32_t p_addr = tmem_base + lane_base + (buf ? kColP1 : kColP0);
-      mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
-      if (tid == 0 && i < 32) WE_TRACE(16 + 4 * i);
+    int j = 0;
+    for (int i = st; i < n; i += 2, ++j) {
+      mbar_wait(&s_ready[st], j & 1, s_abort);   // also means PV(i-2) has completed: O_st is quiescent
+      if (row == 0 && i < 32) WE_TRACE(16 + 4 * i);
       tc_fence_after();
-      uint32_t s[4][32];
-      tmem_ld32(s_addr + 0, s[0]);
-      tmem_ld32(s_addr + 32, s[1]);
-      tmem_ld32(s_addr + 64, s[2]);
-      tmem_ld32(s_addr + 96, s[3]);
-      tmem_ld_wait();
       const uint32_t entry = s_list[t0 + i];
-      if (entry & 1u) {
-        // partial tile: mask tokens that are unwritten, hidden, or beyond the buffer
-        const int key0 = static_cast<int>(entry >> 1) * kBlockN;
+      const bool partial = (entry & 1u) != 0u;
+      const int key0 = static_cast<int>(entry >> 1) * kBlockN;
+      // pass 1: row maximum (four independent max chains; the chunk loop stays rolled to keep the code small)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        tmem_ld32(s_addr + c * 32, s);
+        tmem_ld_wait();
+        if (partial) {
+          const uint32_t vis = chunk_visibility(wr, key0 + c * 32, p.C, hide, slot_base, p.T);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+          for (int e = 0; e < 32; ++e)
+            if (!((vis >> e) & 1u)) s[e] = 0xFF800000u;  // -inf
+        }
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c * 32 + j;
-            bool vis = key < p.C;
-            if (vis) vis = wr[key] != 0 && !(hide && key >= slot_base && key < slot_base + p.T);
-            if (!vis) s[c][j] = 0xFF800000u;  // -inf
-          }
+        for (int e = 0; e < 32; e += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(s[e + 0]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(s[e + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(s[e + 2]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(s[e + 3]));
         }
       }
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(s[c][j]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      if (row == 0 && i < 32) WE_TRACE(17 + 4 * i);
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      if (tid == 0 && i < 32) WE_TRACE(17 + 4 * i);
-      if (i > 0) {
-        mbar_wait(o_ready, (i - 1) & 1, s_abort);  // O holds tiles < i and no MMA is writing it
-        tc_fence_after();
-      }
-      if (tid == 0 && i < 32) WE_TRACE(18 + 4 * i);
       const bool need = (m_new - m_run) > kRescaleThreshold;  // first tile: inf > threshold
       if (__any_sync(0xffffffffu, need)) {
-        const float alpha = exp2f(m_run - m_new);             // first tile: exp2(-inf) = 0
+        const float alpha = fast_exp2(m_run - m_new);         // first tile: exp2(-inf) = 0
         l_run *= alpha;
         m_run = m_new;
-        if (i > 0) {
-#pragma unroll
+        if (j > 0) {
+#pragma unroll 1
           for (int c = 0; c < DH / 32; ++c) {
             uint32_t o[32];
-            tmem_ld32(tmem_base + lane_base + kColO + c * 32, o);
+            tmem_ld32(o_addr + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-            tmem_st32(tmem_base + lane_base + kColO + c * 32, o);
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(o_addr + c * 32, o);
           }
         }
       }
-      float sum = 0.f;
-#pragma unroll
+      if (row == 0 && i < 32) WE_TRACE(18 + 4 * i);
+      // pass 2: P = exp2(S * scale - m), written over the columns of S that were already consumed
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_run;
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        tmem_ld32(s_addr + c * 32, s);
+        tmem_ld_wait();
+        if (partial) {
+          const uint32_t vis = chunk_visibility(wr, key0 + c * 32, p.C, hide, slot_base, p.T);
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (!((vis >> e) & 1u)) s[e] = 0xFF800000u;
+        }
         uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = exp2f(fmaf(__uint_as_float(s[c][2 * j]), p.scale_log2, -m_run));
-          const float p1 = exp2f(fmaf(__uint_as_float(s[c][2 * j + 1]), p.scale_log2, -m_run));
-          sum += p0 + p1;
-          pk[j] = pack2<BF16>(p0, p1);
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * e]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * e + 1]), p.scale_log2, neg_m));
+          sum4[(2 * e) & 3] += p0;
+          sum4[(2 * e + 1) & 3] += p1;
+          pk[e] = pack2<BF16>(p0, p1);
         }
-        tmem_st16(p_addr + c * 16, pk);
+        tmem_st16(s_addr + c * 16, pk);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run += sum;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_ready[buf]);
-      if (tid == 0 && i < 32) WE_TRACE(19 + 4 * i);
+      mbar_arrive(&p_ready[st]);
+      if (row == 0 && i < 32) WE_TRACE(19 + 4 * i);
     }
 
-    // ------------------------------------------------------------ epilogue
-    if (n > 0) {
-      mbar_wait(o_ready, (n - 1) & 1, s_abort);
-      tc_fence_after();
-    }
-    if (tid == 0) WE_TRACE(224);
-    const int unit = (b * p.Hq + h) * p.n_qtiles + qt;
-    if (p.nsplit == 1) {
-      const float inv = 1.0f / l_run;
-      const bool in_range = q0 + row < p.T;
-      uint8_t* orow = static_cast<uint8_t*>(p.out) +
-                      2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2]);
-#pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tmem_base + lane_base + kColO + c * 32, o);
+    // ---------------------------------------------------------- after the last tile
+    // Both streams' accumulators are final once both "last PV" commits have arrived; only then is the
+    // K / V shared memory dead and reusable as the exchange buffer.
+    if (n >= 1) mbar_wait(&o_final[0], 0, s_abort);
+    if (n >= 2) mbar_wait(&o_final[1], 0, s_abort);
+    tc_fence_after();
+    if (row == 0) WE_TRACE(224 + st);
+    // The two streams of the CTA are merged first: exchange (m, l), then each group combines one half of
+    // the head dim straight from tensor memory (group 0 columns [0, DH/2), group 1 the rest).
+    s_ml[(st * 2 + 0) * kBlockM + row] = m_run;
+    s_ml[(st * 2 + 1) * kBlockM + row] = l_run;
+    named_bar_sync(1, kSoftmaxThreads);
+    const float m_other = s_ml[((st ^ 1) * 2 + 0) * kBlockM + row];
+    const float l_other = s_ml[((st ^ 1) * 2 + 1) * kBlockM + row];
+    const float m_a = st == 0 ? m_run : m_other, l_a = st == 0 ? l_run : l_other;
+    const float m_b = st == 0 ? m_other : m_run, l_b = st == 0 ? l_other : l_run;
+    const bool has_a = n >= 1, has_b = n >= 2;
+    const float m_cta = fmaxf(has_a ? m_a : -INFINITY, has_b ? m_b : -INFINITY);
+    const float w_a = has_a ? fast_exp2(m_a - m_cta) : 0.f;
+    const float w_b = has_b ? fast_exp2(m_b - m_cta) : 0.f;
+    const float l_cta = l_a * w_a + l_b * w_b;
+    constexpr int kHalf = DH / 2;
+    const int col0 = st * kHalf;
+    const uint32_t oa_addr = tmem_base + lane_base + kColO + col0;
+    const uint32_t ob_addr = oa_addr + 128u;
+    if (p.cluster_merge) {
+      // The CTA's partial result: O (un-normalised, fp32, row-major with a 4-float pad), m, l.
+      float* part = reinterpret_cast<float*>(sK);
+#pragma unroll 1
+      for (int c = 0; c < kHalf / 32; ++c) {
+        uint32_t oa[32], ob[32];
+        if (has_a) tmem_ld32(oa_addr + c * 32, oa);
+        if (has_b) tmem_ld32(ob_addr + c * 32, ob);
         tmem_ld_wait();
-        if (in_range) {
+        float4* dst = reinterpret_cast<float4*>(part + row * Cfg::kPartRow + col0 + c * 32);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack2<BF16>(__uint_as_float(o[8 * j + 0]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
-            v.y = pack2<BF16>(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
-            v.z = pack2<BF16>(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
-            v.w = pack2<BF16>(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 64 + j * 16) = v;
+        for (int e = 0; e < 8; ++e) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (has_a) {
+            v.x = __uint_as_float(oa[4 * e + 0]) * w_a;
+            v.y = __uint_as_float(oa[4 * e + 1]) * w_a;
+            v.z = __uint_as_float(oa[4 * e + 2]) * w_a;
+            v.w = __uint_as_float(oa[4 * e + 3]) * w_a;
           }
+          if (has_b) {
+            v.x = fmaf(__uint_as_float(ob[4 * e + 0]), w_b, v.x);
+            v.y = fmaf(__uint_as_float(ob[4 * e + 1]), w_b, v.y);
+            v.z = fmaf(__uint_as_float(ob[4 * e + 2]), w_b, v.z);
+            v.w = fmaf(__uint_as_float(ob[4 * e + 3]), w_b, v.w);
+          }
+          dst[e] = v;
         }
       }
+      if (st == 0) {
+        part[row * Cfg::kPartRow + DH] = m_cta;          // -inf and 0 when the split got no tile
+        part[row * Cfg::kPartRow + DH + 1] = l_cta;
+      }
+      fence_proxy_async_smem();        // the rows are read by bulk copies (async proxy) below
+      if (row == 0) WE_TRACE(232 + st);
     } else {
+      // ------------------------------- workspace path: hand the CTA's partial over through global memory
+      float acc[kHalf];
+#pragma unroll
+      for (int c = 0; c < kHalf / 32; ++c) {
+        uint32_t oa[32], ob[32];
+        if (has_a) tmem_ld32(oa_addr + c * 32, oa);
+        if (has_b) tmem_ld32(ob_addr + c * 32, ob);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float va = has_a ? __uint_as_float(oa[e]) * w_a : 0.f;
+          const float vb = has_b ? __uint_as_float(ob[e]) * w_b : 0.f;
+          acc[c * 32 + e] = va + vb;
+        }
+      }
+      const int unit = (b * p.Hq + h) * p.n_qtiles + qt;
+      const bool in_range = q0 + row < p.T;
+      uint8_t* orow = static_cast<uint8_t*>(p.out) +
+                      2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + col0);
       // Partial result of this split, column-major so that the 128 row-threads store coalesced.
       float* wo = p.ws_o + (static_cast<int64_t>(unit) * p.nsplit + split) * (DH * kBlockM);
       float* wml = p.ws_ml + (static_cast<int64_t>(unit) * p.nsplit + split) * (2 * kBlockM);
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t o[32];
-        if (n > 0) {
-          tmem_ld32(tmem_base + lane_base + kColO + c * 32, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0u;
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) __stcg(wo + (c * 32 + j) * kBlockM + row, __uint_as_float(o[j]));
+      for (int e = 0; e < kHalf; ++e) __stcg(wo + (col0 + e) * kBlockM + row, acc[e]);
+      if (st == 0) {
+        __stcg(wml + row, m_cta);
+        __stcg(wml + kBlockM + row, l_cta);
       }
-      __stcg(wml + row, m_run);
-      __stcg(wml + kBlockM + row, l_run);
       __threadfence();
-      named_bar_sync(1, 128);
+      named_bar_sync(1, kSoftmaxThreads);
       if (tid == 0) WE_TRACE(225);
       if (tid == 0) *s_ticket = static_cast<uint32_t>(atomicAdd(p.ws_cnt + unit, 1));
-      named_bar_sync(1, 128);
+      named_bar_sync(1, kSoftmaxThreads);
       if (tid == 0) { WE_TRACE(226); WE_TRACE_VAL(229, *s_ticket); }
       if (*s_ticket == static_cast<uint32_t>(p.nsplit - 1)) {
         // Last split to arrive merges all of them, always in split order (deterministic).
@@ -479,37 +676,126 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float ms = __ldcg(ml0 + s2 * 2 * kBlockM + row);
           if (ls > 0.f) m_all = fmaxf(m_all, ms);
         }
-        float acc[DH];
 #pragma unroll
-        for (int j = 0; j < DH; ++j) acc[j] = 0.f;
+        for (int e = 0; e < kHalf; ++e) acc[e] = 0.f;
         float den = 0.f;
         for (int s2 = 0; s2 < p.nsplit; ++s2) {
           const float ls = __ldcg(ml0 + s2 * 2 * kBlockM + kBlockM + row);
           const float ms = __ldcg(ml0 + s2 * 2 * kBlockM + row);
           if (!(ls > 0.f)) continue;
-          const float wgt = exp2f(ms - m_all);
+          const float wgt = fast_exp2(ms - m_all);
           den += ls * wgt;
-          const float* os2 = o0 + static_cast<int64_t>(s2) * (DH * kBlockM) + row;
+          const float* os2 = o0 + static_cast<int64_t>(s2) * (DH * kBlockM) + col0 * kBlockM + row;
 #pragma unroll
-          for (int j = 0; j < DH; ++j) acc[j] = fmaf(wgt, __ldcg(os2 + j * kBlockM), acc[j]);
+          for (int e = 0; e < kHalf; ++e) acc[e] = fmaf(wgt, __ldcg(os2 + e * kBlockM), acc[e]);
         }
         const float inv = 1.0f / den;
-        if (q0 + row < p.T) {
-          uint8_t* orow = static_cast<uint8_t*>(p.out) +
-                          2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2]);
+        if (in_range) {
 #pragma unroll
-          for (int j = 0; j < DH / 8; ++j) {
+          for (int e = 0; e < kHalf / 8; ++e) {
             uint4 v;
-            v.x = pack2<BF16>(acc[8 * j + 0] * inv, acc[8 * j + 1] * inv);
-            v.y = pack2<BF16>(acc[8 * j + 2] * inv, acc[8 * j + 3] * inv);
-            v.z = pack2<BF16>(acc[8 * j + 4] * inv, acc[8 * j + 5] * inv);
-            v.w = pack2<BF16>(acc[8 * j + 6] * inv, acc[8 * j + 7] * inv);
-            *reinterpret_cast<uint4*>(orow + j * 16) = v;
+            v.x = pack2<BF16>(acc[8 * e + 0] * inv, acc[8 * e + 1] * inv);
+            v.y = pack2<BF16>(acc[8 * e + 2] * inv, acc[8 * e + 3] * inv);
+            v.z = pack2<BF16>(acc[8 * e + 4] * inv, acc[8 * e + 5] * inv);
+            v.w = pack2<BF16>(acc[8 * e + 6] * inv, acc[8 * e + 7] * inv);
+            *reinterpret_cast<uint4*>(orow + e * 16) = v;
           }
         }
         if (tid == 0) p.ws_cnt[unit] = 0;  // leave the counter ready for the next launch
         if (tid == 0) WE_TRACE(227);
       }
+    }
+  }
+
+  // ------------------------------------------------ merge of the splits through cluster shared memory
+  // CTA `split` of the cluster produces rows [r0, r1) of the query tile.  Every CTA pushes, with one bulk
+  // copy per peer, the rows a peer owns from its own partial tile into that peer's receive buffer (the idle
+  // V ring); the owner then reduces its own rows and the received ones, always in split order, so reruns
+  // are bit-identical.  A launch without splits is a cluster of one and only normalises its own rows.
+  if (p.cluster_merge) {
+    const int ns = p.nsplit;
+    const int r0 = (kBlockM * split) / ns, r1 = (kBlockM * (split + 1)) / ns;
+    const int R = r1 - r0;
+    float* part = reinterpret_cast<float*>(sK);
+    float* recv = reinterpret_cast<float*>(sV);
+    const int slot_floats = R * Cfg::kPartRow;
+    if (tid == 0) WE_TRACE(234);
+    if (ns > 1) {
+      if (tid == 0) mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((ns - 1) * slot_floats * 4));
+      cluster_arrive_release();
+      cluster_wait_acquire();         // every CTA has left its main loop: its V ring may be written
+      if (tid == 0) {
+        WE_TRACE(235);
+        for (int d = 0; d < ns; ++d) {
+          if (d == split) continue;
+          const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
+          const int my_slot = split < d ? split : split - 1;          // my position among d's peers
+          const uint32_t dst = dsmem_addr(smem_u32(sV) + static_cast<uint32_t>(my_slot * (d1 - d0) * Cfg::kPartRow * 4),
+                                          static_cast<uint32_t>(d));
+          const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
+          bulk_copy_to_peer(dst, smem_u32(part + d0 * Cfg::kPartRow), static_cast<uint32_t>((d1 - d0) * Cfg::kPartRow * 4),
+                            bar);
+        }
+      }
+      mbar_wait(recv_bar, 0, s_abort);   // the rows of all peers have landed
+    }
+    if (tid == 0) WE_TRACE(236);
+    // One item = one row x 4 consecutive columns; consecutive lanes take consecutive columns of a row.
+    constexpr int kGroups = DH / 4;
+    const int items = R * kGroups;
+#ifdef WE_ATTN_DEBUG
+#pragma unroll 1
+    for (int rep = 0; rep < (trace != nullptr ? 2 : 1); ++rep) {
+    if (tid == 0 && rep == 1) WE_TRACE(238);
+#endif
+#pragma unroll 1
+    for (int it = tid; it < items; it += kAttnThreads) {
+      const int rl = it / kGroups;
+      const int c0 = (it - rl * kGroups) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float den = 0.f;
+      float m_all = -INFINITY;
+      float4 v[8];
+      float ms[8], ls[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int pp = u < ns ? u : split;                        // ns <= 8; surplus lanes re-read the own row
+        const float* src = pp == split ? part + (r0 + rl) * Cfg::kPartRow
+                                       : recv + (pp < split ? pp : pp - 1) * slot_floats + rl * Cfg::kPartRow;
+        v[u] = *reinterpret_cast<const float4*>(src + c0);
+        ms[u] = src[DH];
+        ls[u] = u < ns ? src[DH + 1] : 0.f;
+        if (ls[u] > 0.f) m_all = fmaxf(m_all, ms[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (ls[u] > 0.f) {                                         // splits without tiles hold stale rows
+          const float wgt = fast_exp2(ms[u] - m_all);
+          den += ls[u] * wgt;
+          acc.x = fmaf(wgt, v[u].x, acc.x);
+          acc.y = fmaf(wgt, v[u].y, acc.y);
+          acc.z = fmaf(wgt, v[u].z, acc.z);
+          acc.w = fmaf(wgt, v[u].w, acc.w);
+        }
+      }
+      const int row = r0 + rl;
+      if (q0 + row < p.T) {
+        const float inv = 1.0f / den;
+        uint8_t* o = static_cast<uint8_t*>(p.out) +
+                     2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + c0);
+        uint2 v2;
+        v2.x = pack2<BF16>(acc.x * inv, acc.y * inv);
+        v2.y = pack2<BF16>(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(o) = v2;
+      }
+    }
+#ifdef WE_ATTN_DEBUG
+    }
+#endif
+    if (tid == 0) WE_TRACE(237);
+    if (ns > 1) {
+      cluster_arrive_release();
+      cluster_wait_acquire();         // all copies have been consumed: sources and receive buffers may go away
     }
   }
 
@@ -522,7 +808,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __nanosleep(1000000);  // let copies and MMAs that are still in flight land before the CTA goes away
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -616,8 +902,40 @@ static SplitPlan plan_splits(int B, int Hq, int T, int Dh, int64_t L) {
   return s;
 }
 
+// How many clusters of `cluster` CTAs of this kernel can be resident at once on the current device
+// (cached per device and cluster size; 0 = clusters of that size cannot be launched).
 template <int DH, bool BF16>
-static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p,
+static int max_active_clusters(int cluster) {
+  static int cached[64][9];
+  static bool known[64][9] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return 0;
+  if (!known[dev][cluster]) {
+    using Cfg = AttnCfg<DH>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(cluster) * 64u, 1, 1);
+    cfg.blockDim = dim3(kAttnThreads, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, frame_attn_kernel<DH, BF16>, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = 0;
+    }
+    cached[dev][cluster] = n;
+    known[dev][cluster] = true;
+  }
+  return cached[dev][cluster];
+}
+
+template <int DH, bool BF16>
+static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnParams p,
                           dim3 grid, cudaStream_t stream) {
   using Cfg = AttnCfg<DH>;
   static bool attr_done[64] = {false};
@@ -629,10 +947,30 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_done[dev] = true;
   }
-  frame_attn_kernel<DH, BF16><<<grid, kAttnThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, p);
+  // Splits of one query tile merge through cluster shared memory when they fit a portable cluster and all
+  // clusters of the launch can be resident at once; otherwise through the caller's workspace.
+  const int units = static_cast<int>(grid.x / static_cast<unsigned>(p.nsplit)) * static_cast<int>(grid.y * grid.z);
+  p.cluster_merge = 0;
+  if (p.nsplit == 1 || (p.nsplit <= 8 && max_active_clusters<DH, BF16>(p.nsplit) >= units)) p.cluster_merge = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kAttnThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (p.cluster_merge) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(p.nsplit);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, frame_attn_kernel<DH, BF16>, tq, tk, tv, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? WE_B200_OK : static_cast<int>(e);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const cudaError_t e2 = cudaGetLastError();
+  return e2 == cudaSuccess ? WE_B200_OK : static_cast<int>(e2);
 }
 
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
@@ -674,6 +1012,7 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   p.Hkv = g->Hkv;
   p.dilation = g->dilation;
   p.ntiles = sp.ntiles;
+  p.ring_frames = static_cast<int32_t>(g->L / g->T);
   p.nsplit = sp.nsplit;
   p.n_qtiles = sp.n_qtiles;
   p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf(static_cast<float>(g->Dh))) * 1.4426950408889634f;
@@ -690,6 +1029,7 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   const uint8_t* v_base = static_cast<const uint8_t*>(kv) + 2 * g->kv_plane_stride;
   if ((rc = make_map(&tv, v_base, g->dtype, C, g->Hkv, g->B, g->Dh, kvs, perm_v)) != WE_B200_OK) return rc;
 
+  p.cluster_merge = 0;
   dim3 grid(static_cast<unsigned>(sp.n_qtiles * sp.nsplit), static_cast<unsigned>(Hq), static_cast<unsigned>(g->B));
   if (g->Dh == 128) {
     return g->dtype == WE_B200_BF16 ? launch_variant<128, true>(tq, tk, tv, p, grid, stream)
@@ -702,10 +1042,6 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
 }  // namespace we
 
 #ifdef WE_ATTN_DEBUG
-extern "C" __attribute__((visibility("default"))) int we_b200_debug_set(int idx, uint32_t value) {
-  if (idx < 0 || idx >= 8) return -1;
-  return static_cast<int>(cudaMemcpyToSymbol(we::g_dbg, &value, sizeof(value), idx * sizeof(uint32_t)));
-}
 // Buffer of 64 x 256 uint32 for the per-CTA timeline (null switches tracing off).
 extern "C" __attribute__((visibility("default"))) int we_b200_debug_trace(uint32_t* buf) {
   return static_cast<int>(cudaMemcpyToSymbol(we::g_trace, &buf, sizeof(buf)));
