@@ -48,5 +48,5 @@ extern "C" int we_b200_append_attend(const void* q, const int64_t* q_strides_hos
                                       frame_t, geom_host, is_frozen, s);
   if (rc != WE_B200_OK) return rc;
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               workspace, workspace_bytes, status, s);
+                               workspace, workspace_bytes, status, /*after_append=*/true, s);
 }

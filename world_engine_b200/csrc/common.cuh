@@ -70,6 +70,7 @@ int kv_append_launch(const void* k_new, const int64_t* ks, const void* v_new, co
 
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
                       const uint8_t* written, const int64_t* frame_t, const we_b200_cache_geom* g, float scale,
-                      void* workspace, size_t workspace_bytes, int32_t* status, cudaStream_t stream);
+                      void* workspace, size_t workspace_bytes, int32_t* status, bool after_append,
+                      cudaStream_t stream);
 
 }  // namespace we

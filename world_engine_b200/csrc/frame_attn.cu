@@ -187,6 +187,10 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   return v;
 }
 
+// Programmatic dependent launch: wait until the preceding kernel of the stream has completed and its
+// writes are visible (returns at once when the launch carried no programmatic dependency).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Is token `key` visible to this call?  (written, not in the hidden slot, inside the buffer.)
 __device__ __forceinline__ bool token_visible(const uint8_t* wr, int key, int C, bool hide, int64_t slot_base, int T) {
   if (key >= C) return false;
@@ -398,6 +402,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
   // ------------------------------------------------------------------ roles
+  if (warp == 8 || warp == 10) {
+    // Everything above only needed data that existed before the preceding kernel of the stream (the
+    // append of this frame, when launched through we_b200_append_attend) began.  The cache contents it
+    // writes are needed from here on.
+    grid_dependency_wait();
+  }
   if (warp == 8) {
     if (lane == 0) {
       // K ring: K(i) is issued as soon as S(i - kStagesK) has consumed its stage.
@@ -740,58 +750,65 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(recv_bar, 0, s_abort);   // the rows of all peers have landed
     }
     if (tid == 0) WE_TRACE(236);
+    // Per (split, row) weight exp2(m - m_row) / l_row, computed once per row by one thread.
+    float* wtab = recv + (ns - 1) * slot_floats;                 // [ns][R], behind the receive slots
+    auto partial_row = [&](int pp, int rl) -> const float* {
+      return pp == split ? part + (r0 + rl) * Cfg::kPartRow
+                         : recv + (pp < split ? pp : pp - 1) * slot_floats + rl * Cfg::kPartRow;
+    };
+#pragma unroll 1
+    for (int rl = tid; rl < R; rl += kAttnThreads) {
+      float m_all = -INFINITY;
+#pragma unroll 1
+      for (int pp = 0; pp < ns; ++pp) {
+        const float* src = partial_row(pp, rl);
+        if (src[DH + 1] > 0.f) m_all = fmaxf(m_all, src[DH]);
+      }
+      float den = 0.f;
+#pragma unroll 1
+      for (int pp = 0; pp < ns; ++pp) {
+        const float* src = partial_row(pp, rl);
+        const float ls = src[DH + 1];
+        const float wgt = ls > 0.f ? fast_exp2(src[DH] - m_all) : 0.f;   // splits without tiles weigh nothing
+        den += ls * wgt;
+        wtab[pp * R + rl] = wgt;
+      }
+      const float inv = 1.0f / den;
+#pragma unroll 1
+      for (int pp = 0; pp < ns; ++pp) wtab[pp * R + rl] *= inv;
+    }
+    __syncthreads();
     // One item = one row x 4 consecutive columns; consecutive lanes take consecutive columns of a row.
     constexpr int kGroups = DH / 4;
     const int items = R * kGroups;
-#ifdef WE_ATTN_DEBUG
-#pragma unroll 1
-    for (int rep = 0; rep < (trace != nullptr ? 2 : 1); ++rep) {
-    if (tid == 0 && rep == 1) WE_TRACE(238);
-#endif
 #pragma unroll 1
     for (int it = tid; it < items; it += kAttnThreads) {
       const int rl = it / kGroups;
       const int c0 = (it - rl * kGroups) * 4;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      float den = 0.f;
-      float m_all = -INFINITY;
-      float4 v[8];
-      float ms[8], ls[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int pp = u < ns ? u : split;                        // ns <= 8; surplus lanes re-read the own row
-        const float* src = pp == split ? part + (r0 + rl) * Cfg::kPartRow
-                                       : recv + (pp < split ? pp : pp - 1) * slot_floats + rl * Cfg::kPartRow;
-        v[u] = *reinterpret_cast<const float4*>(src + c0);
-        ms[u] = src[DH];
-        ls[u] = u < ns ? src[DH + 1] : 0.f;
-        if (ls[u] > 0.f) m_all = fmaxf(m_all, ms[u]);
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (ls[u] > 0.f) {                                         // splits without tiles hold stale rows
-          const float wgt = fast_exp2(ms[u] - m_all);
-          den += ls[u] * wgt;
-          acc.x = fmaf(wgt, v[u].x, acc.x);
-          acc.y = fmaf(wgt, v[u].y, acc.y);
-          acc.z = fmaf(wgt, v[u].z, acc.z);
-          acc.w = fmaf(wgt, v[u].w, acc.w);
+        if (u < ns) {
+          const float wgt = wtab[u * R + rl];
+          if (wgt != 0.f) {                                        // never touch the stale rows of an empty split
+            const float4 v = *reinterpret_cast<const float4*>(partial_row(u, rl) + c0);
+            acc.x = fmaf(wgt, v.x, acc.x);
+            acc.y = fmaf(wgt, v.y, acc.y);
+            acc.z = fmaf(wgt, v.z, acc.z);
+            acc.w = fmaf(wgt, v.w, acc.w);
+          }
         }
       }
       const int row = r0 + rl;
       if (q0 + row < p.T) {
-        const float inv = 1.0f / den;
         uint8_t* o = static_cast<uint8_t*>(p.out) +
                      2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + c0);
         uint2 v2;
-        v2.x = pack2<BF16>(acc.x * inv, acc.y * inv);
-        v2.y = pack2<BF16>(acc.z * inv, acc.w * inv);
+        v2.x = pack2<BF16>(acc.x, acc.y);
+        v2.y = pack2<BF16>(acc.z, acc.w);
         *reinterpret_cast<uint2*>(o) = v2;
       }
     }
-#ifdef WE_ATTN_DEBUG
-    }
-#endif
     if (tid == 0) WE_TRACE(237);
     if (ns > 1) {
       cluster_arrive_release();
@@ -936,7 +953,7 @@ static int max_active_clusters(int cluster) {
 
 template <int DH, bool BF16>
 static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnParams p,
-                          dim3 grid, cudaStream_t stream) {
+                          dim3 grid, bool overlap_previous_kernel, cudaStream_t stream) {
   using Cfg = AttnCfg<DH>;
   static bool attr_done[64] = {false};
   int dev = 0;
@@ -957,15 +974,24 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   cfg.blockDim = dim3(kAttnThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  unsigned n_attr = 0;
   if (p.cluster_merge) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(p.nsplit);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = static_cast<unsigned>(p.nsplit);
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
+  if (overlap_previous_kernel) {
+    // Programmatic dependent launch: the CTAs may start while the preceding kernel of the stream (the append)
+    // is still draining; the kernel waits for it (griddepcontrol.wait) before it touches the cache contents.
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = n_attr ? attr : nullptr;
+  cfg.numAttrs = n_attr;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, frame_attn_kernel<DH, BF16>, tq, tk, tv, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -975,7 +1001,8 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
 
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
                       const uint8_t* written, const int64_t* frame_t, const we_b200_cache_geom* g, float scale,
-                      void* workspace, size_t workspace_bytes, int32_t* status, cudaStream_t stream) {
+                      void* workspace, size_t workspace_bytes, int32_t* status, bool after_append,
+                      cudaStream_t stream) {
   if (!q || !out || !kv || !written || !frame_t) return WE_B200_E_NULL;
   int rc = check_geom(g);
   if (rc != WE_B200_OK) return rc;
@@ -1032,11 +1059,11 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   p.cluster_merge = 0;
   dim3 grid(static_cast<unsigned>(sp.n_qtiles * sp.nsplit), static_cast<unsigned>(Hq), static_cast<unsigned>(g->B));
   if (g->Dh == 128) {
-    return g->dtype == WE_B200_BF16 ? launch_variant<128, true>(tq, tk, tv, p, grid, stream)
-                                    : launch_variant<128, false>(tq, tk, tv, p, grid, stream);
+    return g->dtype == WE_B200_BF16 ? launch_variant<128, true>(tq, tk, tv, p, grid, after_append, stream)
+                                    : launch_variant<128, false>(tq, tk, tv, p, grid, after_append, stream);
   }
-  return g->dtype == WE_B200_BF16 ? launch_variant<64, true>(tq, tk, tv, p, grid, stream)
-                                  : launch_variant<64, false>(tq, tk, tv, p, grid, stream);
+  return g->dtype == WE_B200_BF16 ? launch_variant<64, true>(tq, tk, tv, p, grid, after_append, stream)
+                                  : launch_variant<64, false>(tq, tk, tv, p, grid, after_append, stream);
 }
 
 }  // namespace we
@@ -1059,7 +1086,7 @@ extern "C" int we_b200_frame_attn(const void* q, const int64_t* q_strides_host, 
                                   const int64_t* frame_t, const we_b200_cache_geom* geom_host, float scale,
                                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+                               workspace, workspace_bytes, status, false, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------- entry point that allocates nothing
@@ -1109,5 +1136,5 @@ extern "C" int we_b200_frame_attn_static(const void* q, const int64_t* q_strides
   e = cudaMemsetAsync(scratch, 0, sp.cnt_bytes, s);
   if (e != cudaSuccess) return static_cast<int>(e);
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               scratch, we::kStaticScratchBytes, status, s);
+                               scratch, we::kStaticScratchBytes, status, false, s);
 }

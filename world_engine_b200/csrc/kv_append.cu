@@ -37,6 +37,9 @@ __global__ void __launch_bounds__(kAppendThreads) kv_append_kernel(const AppendP
   __shared__ int64_t s_base;
   __shared__ int s_ring;  // 1 when this call also persists into the ring slot
 
+  // Let a kernel launched with a programmatic dependency on this one (the attention of the same layer-step)
+  // begin its prologue now; it waits for this grid to finish before it reads what is written here.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int plane = blockIdx.y / p.B;
   const int b = blockIdx.y - plane * p.B;
   if (threadIdx.x == 0) {
