@@ -58,8 +58,9 @@ constexpr int kAttnThreads = 384;
 constexpr int kSoftmaxThreads = 256;
 constexpr int kMaxSplits = 32;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0;    // + 128 * stream
-constexpr uint32_t kColO = 256;  // + 128 * stream
+constexpr uint32_t kColS = 0;    // + 128 * (tile & 1)
+constexpr uint32_t kColO = 256;
+constexpr uint32_t kColP = 384;  // + 64 * (tile & 1)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int DH>
@@ -70,7 +71,7 @@ struct AttnCfg {
   static constexpr int kStagesK = DH == 128 ? 3 : 4;      // stage counts also keep smem above half an SM,
   static constexpr int kStagesV = DH == 128 ? 2 : 4;      // so two CTAs never share an SM's tensor memory
   static constexpr int kSmemTiles = kTileBytes * (1 + kStagesK + kStagesV);
-  static constexpr int kSmemAux = 64 * 8 + kMaxTiles * 2 + 64 + 4 * kBlockM * 4 + kMaxTiles;
+  static constexpr int kSmemAux = 64 * 8 + kMaxTiles * 2 + 64 + 4 * kBlockM * 4 + kMaxTiles + 8 * kBlockM * 8;
   static constexpr int kSmemBytes = kSmemTiles + kSmemAux + 1024;  // + slack for 1024-byte alignment
   // Exchange buffers of the epilogue, laid over the (then idle) rings: the CTA's partial O tile
   // [128][DH + 4] fp32 over the K ring (row maximum and row sum in the first two pad columns), and the
@@ -173,6 +174,9 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uin
       "r"(src_cta_addr), "r"(bytes), "r"(bar_cluster_addr)
       : "memory");
 }
+__device__ __forceinline__ void st_dsmem_f32x2(uint32_t addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
 __device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -248,7 +252,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* recv_bar = bars + 1;  // incoming partial rows of the split merge
   uint64_t* s_ready = bars + 2;   // [2] per stream
   uint64_t* p_ready = bars + 4;   // [2]
-  uint64_t* o_final = bars + 6;   // [2]
+  uint64_t* o_ready = bars + 6;   // one phase per tile: PV(i) complete
   uint64_t* k_full = bars + 8;                  // [kStagesK]
   uint64_t* k_empty = k_full + kStagesK;        // [kStagesK]
   uint64_t* v_full = k_empty + kStagesK;        // [kStagesV]
@@ -261,7 +265,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint32_t* s_ticket = s_misc + 3;
   volatile int64_t* s_slot = reinterpret_cast<volatile int64_t*>(s_misc + 4);  // [0] base, [1] hide flag
   float* s_ml = reinterpret_cast<float*>(s_misc + 16);                // [stream][m, l][128]
-  uint8_t* s_cnt = reinterpret_cast<uint8_t*>(s_ml + 4 * kBlockM);    // [kMaxTiles] visible keys per tile (128 -> 128)
+  float* s_x = s_ml;                                                  // [tile & 1][group][128] half-row exchange
+  uint8_t* s_cnt = reinterpret_cast<uint8_t*>(s_ml + 4 * kBlockM);    // [kMaxTiles] visible keys per tile
+  float* s_mltab = reinterpret_cast<float*>(s_cnt + kMaxTiles);       // [8 splits][128 rows][m, l]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -301,9 +307,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(recv_bar, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_ready[s], 1);
-      mbar_init(&p_ready[s], 128);
-      mbar_init(&o_final[s], 1);
+      mbar_init(&p_ready[s], kSoftmaxThreads);
     }
+    mbar_init(o_ready, 1);
     for (int s = 0; s < kStagesK; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -446,7 +452,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t k_addr = smem_u32(sK);
       const uint32_t v_addr = smem_u32(sV);
       mbar_wait(q_full, 0, s_abort);
-      // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; goes to stream i & 1.
+      // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; into S buffer i & 1.
       auto issue_s = [&](int i) {
         const int sk = i % kStagesK;
         mbar_wait(&k_full[sk], (i / kStagesK) & 1, s_abort);
@@ -463,81 +469,114 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_commit(&s_ready[i & 1]);
       };
       issue_s(0);
-      if (n > 1) issue_s(1);
       for (int i = 0; i < n; ++i) {
-        const int st = i & 1;
         const int sv = i % kStagesV;
-        mbar_wait(&p_ready[st], (i >> 1) & 1, s_abort);
+        // S(i+1) goes first: its buffer was released when P(i-1) was handed over, and the tensor pipe
+        // computes it while the softmax warps are busy with S(i).
+        if (i + 1 < n) issue_s(i + 1);
+        mbar_wait(&p_ready[i & 1], (i >> 1) & 1, s_abort);
         if (i < 24) WE_TRACE(144 + 2 * i);
         mbar_wait(&v_full[sv], (i / kStagesV) & 1, s_abort);
         if (i < 24) WE_TRACE(145 + 2 * i);
         tc_fence_after();
-        // O_st += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16.  P sits in the first 64
-        // columns of S_st (two bf16 per column).
-        const uint32_t d = tmem_base + kColO + 128u * st;
-        const uint32_t a_t = tmem_base + kColS + 128u * st;
+        // O += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16 (two bf16 of P per TMEM column).
+        const uint32_t d = tmem_base + kColO;
+        const uint32_t a_t = tmem_base + kColP + 64u * (i & 1);
 #pragma unroll
         for (int kk = 0; kk < kBlockN / 16; ++kk) {
           const uint64_t bd = umma_desc_sw128(v_addr + sv * Cfg::kTileBytes + kk * 2048, Cfg::kChunkBytes, 1024);
-          umma_ts(d, a_t + kk * 8, bd, kIdescPV, (i >= 2 || kk > 0) ? 1u : 0u);
+          umma_ts(d, a_t + kk * 8, bd, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
         }
         tc_commit(&v_empty[sv]);
-        if (i + 2 >= n) tc_commit(&o_final[st]);   // last tile of this stream
-        if (i + 2 < n) issue_s(i + 2);             // overwrites S_st / P(i): ordered behind PV(i) in the pipe
+        tc_commit(o_ready);
       }
     }
     __syncwarp();
   } else if (warp < 8) {
     // ------------------------------------------------------- softmax warps
-    const int st = warp >> 2;            // stream: 0 = even tiles, 1 = odd tiles
+    // Both groups own all 128 rows; group g handles keys [64g, 64g+64) of every tile and, in the epilogue
+    // and in rescales, columns [DH/2 * g, DH/2 * (g+1)) of O.
+    const int wg = warp >> 2;
     const int row = tid & 127;           // query row within the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * st;
-    const uint32_t o_addr = tmem_base + lane_base + kColO + 128u * st;
-    const int64_t slot_base = s_slot[0];
+    constexpr int kHalf = DH / 2;
+    const int col0 = wg * kHalf;
+    const uint32_t o_addr = tmem_base + lane_base + kColO + col0;
+    const int slot_base = static_cast<int>(s_slot[0]);
     const bool hide = s_slot[1] != 0;
     float m_run = -INFINITY;  // running row maximum, log2 domain, possibly stale by <= threshold
-    float l_run = 0.f;
-    int j = 0;
-    for (int i = st; i < n; i += 2, ++j) {
-      mbar_wait(&s_ready[st], j & 1, s_abort);   // also means PV(i-2) has completed: O_st is quiescent
-      if (row == 0 && i < 32) WE_TRACE(16 + 4 * i);
+    float l_part = 0.f;       // row sum over this group's keys
+    for (int i = 0; i < n; ++i) {
+      const int buf = i & 1;
+      const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
+      const uint32_t p_addr = tmem_base + lane_base + kColP + 64u * buf + 32u * wg;
+      mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
+      if (row == 0 && i < 32) WE_TRACE(16 + 4 * i + 2 * wg);
       tc_fence_after();
+      uint32_t s[2][32];
+      tmem_ld32(s_addr, s[0]);
+      tmem_ld32(s_addr + 32, s[1]);
+      tmem_ld_wait();
       const uint32_t entry = s_list[t0 + i];
-      const bool partial = (entry & 1u) != 0u;
-      const int key0 = static_cast<int>(entry >> 1) * kBlockN;
-      // pass 1: row maximum (four independent max chains; the chunk loop stays rolled to keep the code small)
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld32(s_addr + c * 32, s);
-        tmem_ld_wait();
-        if (partial) {
+      if (entry & 1u) {
+        // partial tile: mask tokens that are unwritten, hidden, or beyond the buffer
+        const int key0 = static_cast<int>(entry >> 1) * kBlockN + 64 * wg;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
           const uint32_t vis = chunk_visibility(wr, key0 + c * 32, p.C, hide, slot_base, p.T);
 #pragma unroll
           for (int e = 0; e < 32; ++e)
-            if (!((vis >> e) & 1u)) s[e] = 0xFF800000u;  // -inf
-        }
-#pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          mx4[0] = fmaxf(mx4[0], __uint_as_float(s[e + 0]));
-          mx4[1] = fmaxf(mx4[1], __uint_as_float(s[e + 1]));
-          mx4[2] = fmaxf(mx4[2], __uint_as_float(s[e + 2]));
-          mx4[3] = fmaxf(mx4[3], __uint_as_float(s[e + 3]));
+            if (!((vis >> e) & 1u)) s[c][e] = 0xFF800000u;  // -inf
         }
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      if (row == 0 && i < 32) WE_TRACE(17 + 4 * i);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int e = 0; e < 32; e += 4) {
+          mx4[0] = fmaxf(mx4[0], __uint_as_float(s[c][e + 0]));
+          mx4[1] = fmaxf(mx4[1], __uint_as_float(s[c][e + 1]));
+          mx4[2] = fmaxf(mx4[2], __uint_as_float(s[c][e + 2]));
+          mx4[3] = fmaxf(mx4[3], __uint_as_float(s[c][e + 3]));
+        }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // the other group holds the other 64 keys of the same rows: exchange the half-row maxima
+      s_x[(buf * 2 + wg) * kBlockM + row] = mx;
+      named_bar_sync(1, kSoftmaxThreads);
+      mx = fmaxf(mx, s_x[(buf * 2 + (wg ^ 1)) * kBlockM + row]);
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       const bool need = (m_new - m_run) > kRescaleThreshold;  // first tile: inf > threshold
-      if (__any_sync(0xffffffffu, need)) {
-        const float alpha = fast_exp2(m_run - m_new);         // first tile: exp2(-inf) = 0
-        l_run *= alpha;
+      float alpha = 1.f;
+      const bool raise = __any_sync(0xffffffffu, need);        // same verdict in both groups (same rows, same data)
+      if (raise) {
+        alpha = fast_exp2(m_run - m_new);                       // first tile: exp2(-inf) = 0
+        l_part *= alpha;
         m_run = m_new;
-        if (j > 0) {
+      }
+      const float neg_m = -m_run;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][2 * e]), p.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][2 * e + 1]), p.scale_log2, neg_m));
+          sum4[(2 * e) & 3] += p0;
+          sum4[(2 * e + 1) & 3] += p1;
+          pk[c * 16 + e] = pack2<BF16>(p0, p1);
+        }
+      tmem_st32(p_addr, pk);
+      l_part += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
+      if (i > 0) {
+        // PV(i-1) has long been issued; its completion makes O safe to touch and is awaited every tile so
+        // that no phase of the barrier is ever skipped.
+        mbar_wait(o_ready, (i - 1) & 1, s_abort);
+        if (raise) {
+          tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < DH / 32; ++c) {
+          for (int c = 0; c < kHalf / 32; ++c) {
             uint32_t o[32];
             tmem_ld32(o_addr + c * 32, o);
             tmem_ld_wait();
@@ -547,134 +586,133 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       }
-      if (row == 0 && i < 32) WE_TRACE(18 + 4 * i);
-      // pass 2: P = exp2(S * scale - m), written over the columns of S that were already consumed
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_run;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld32(s_addr + c * 32, s);
-        tmem_ld_wait();
-        if (partial) {
-          const uint32_t vis = chunk_visibility(wr, key0 + c * 32, p.C, hide, slot_base, p.T);
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (!((vis >> e) & 1u)) s[e] = 0xFF800000u;
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * e]), p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * e + 1]), p.scale_log2, neg_m));
-          sum4[(2 * e) & 3] += p0;
-          sum4[(2 * e + 1) & 3] += p1;
-          pk[e] = pack2<BF16>(p0, p1);
-        }
-        tmem_st16(s_addr + c * 16, pk);
-      }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      l_run += sum;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_ready[st]);
-      if (row == 0 && i < 32) WE_TRACE(19 + 4 * i);
+      mbar_arrive(&p_ready[buf]);
     }
 
     // ---------------------------------------------------------- after the last tile
-    // Both streams' accumulators are final once both "last PV" commits have arrived; only then is the
-    // K / V shared memory dead and reusable as the exchange buffer.
-    if (n >= 1) mbar_wait(&o_final[0], 0, s_abort);
-    if (n >= 2) mbar_wait(&o_final[1], 0, s_abort);
-    tc_fence_after();
-    if (row == 0) WE_TRACE(224 + st);
-    // The two streams of the CTA are merged first: exchange (m, l), then each group combines one half of
-    // the head dim straight from tensor memory (group 0 columns [0, DH/2), group 1 the rest).
-    s_ml[(st * 2 + 0) * kBlockM + row] = m_run;
-    s_ml[(st * 2 + 1) * kBlockM + row] = l_run;
+    if (n > 0) {
+      mbar_wait(o_ready, (n - 1) & 1, s_abort);
+      tc_fence_after();
+    }
+    if (row == 0) WE_TRACE(224 + wg);
+    // total row sum = sum of the two groups' halves
+    s_x[wg * kBlockM + row] = l_part;
     named_bar_sync(1, kSoftmaxThreads);
-    const float m_other = s_ml[((st ^ 1) * 2 + 0) * kBlockM + row];
-    const float l_other = s_ml[((st ^ 1) * 2 + 1) * kBlockM + row];
-    const float m_a = st == 0 ? m_run : m_other, l_a = st == 0 ? l_run : l_other;
-    const float m_b = st == 0 ? m_other : m_run, l_b = st == 0 ? l_other : l_run;
-    const bool has_a = n >= 1, has_b = n >= 2;
-    const float m_cta = fmaxf(has_a ? m_a : -INFINITY, has_b ? m_b : -INFINITY);
-    const float w_a = has_a ? fast_exp2(m_a - m_cta) : 0.f;
-    const float w_b = has_b ? fast_exp2(m_b - m_cta) : 0.f;
-    const float l_cta = l_a * w_a + l_b * w_b;
-    constexpr int kHalf = DH / 2;
-    const int col0 = st * kHalf;
-    const uint32_t oa_addr = tmem_base + lane_base + kColO + col0;
-    const uint32_t ob_addr = oa_addr + 128u;
+    const float l_cta = l_part + s_x[(wg ^ 1) * kBlockM + row];   // 0 when the split got no tile
+    const float m_cta = m_run;                                     // -inf when the split got no tile
+    const bool in_range = q0 + row < p.T;
+    uint8_t* orow = static_cast<uint8_t*>(p.out) +
+                    2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + col0);
     if (p.cluster_merge) {
-      // The CTA's partial result: O (un-normalised, fp32, row-major with a 4-float pad), m, l.
-      float* part = reinterpret_cast<float*>(sK);
-#pragma unroll 1
-      for (int c = 0; c < kHalf / 32; ++c) {
-        uint32_t oa[32], ob[32];
-        if (has_a) tmem_ld32(oa_addr + c * 32, oa);
-        if (has_b) tmem_ld32(ob_addr + c * 32, ob);
-        tmem_ld_wait();
-        float4* dst = reinterpret_cast<float4*>(part + row * Cfg::kPartRow + col0 + c * 32);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (has_a) {
-            v.x = __uint_as_float(oa[4 * e + 0]) * w_a;
-            v.y = __uint_as_float(oa[4 * e + 1]) * w_a;
-            v.z = __uint_as_float(oa[4 * e + 2]) * w_a;
-            v.w = __uint_as_float(oa[4 * e + 3]) * w_a;
-          }
-          if (has_b) {
-            v.x = fmaf(__uint_as_float(ob[4 * e + 0]), w_b, v.x);
-            v.y = fmaf(__uint_as_float(ob[4 * e + 1]), w_b, v.y);
-            v.z = fmaf(__uint_as_float(ob[4 * e + 2]), w_b, v.z);
-            v.w = fmaf(__uint_as_float(ob[4 * e + 3]), w_b, v.w);
-          }
-          dst[e] = v;
+      // Weight of this split's row in the final result: exp2(m - m_row) / l_row over all splits.
+      float wgt;
+      if (p.nsplit == 1) {
+        wgt = 1.0f / l_cta;
+      } else {
+        // announce the bytes the peers will push into this CTA's receive buffer (before any of them can start)
+        if (tid == 0) {
+          const int rows_mine = (kBlockM * (split + 1)) / p.nsplit - (kBlockM * split) / p.nsplit;
+          mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRow * 4));
         }
+        // every CTA of the cluster learns every split's (m, l): group 0 stores its rows' pair into all peers
+        if (wg == 0) {
+          const uint32_t mine = smem_u32(s_mltab + (split * kBlockM + row) * 2);
+          for (int d = 0; d < p.nsplit; ++d) {
+            const uint32_t dst = dsmem_addr(mine, static_cast<uint32_t>(d));
+            st_dsmem_f32x2(dst, m_cta, l_cta);
+          }
+        }
+        cluster_arrive_release();
+        cluster_wait_acquire();       // X: all main loops are over (V rings are free) and all pairs are in place
+        float m_all = -INFINITY;
+#pragma unroll 1
+        for (int s2 = 0; s2 < p.nsplit; ++s2) {
+          const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (s2 * kBlockM + row) * 2);
+          if (ml.y > 0.f) m_all = fmaxf(m_all, ml.x);
+        }
+        float den = 0.f;
+#pragma unroll 1
+        for (int s2 = 0; s2 < p.nsplit; ++s2) {
+          const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (s2 * kBlockM + row) * 2);
+          if (ml.y > 0.f) den += ml.y * fast_exp2(ml.x - m_all);
+        }
+        wgt = l_cta > 0.f ? fast_exp2(m_cta - m_all) / den : 0.f;
       }
-      if (st == 0) {
-        part[row * Cfg::kPartRow + DH] = m_cta;          // -inf and 0 when the split got no tile
-        part[row * Cfg::kPartRow + DH + 1] = l_cta;
+      if (row == 0) WE_TRACE(232 + wg);
+      if (p.nsplit == 1) {
+        // no peers: normalise and store this thread's half row directly
+#pragma unroll 1
+        for (int c = 0; c < kHalf / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
+          if (in_range) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              uint4 v;
+              v.x = pack2<BF16>(__uint_as_float(o[8 * e + 0]) * wgt, __uint_as_float(o[8 * e + 1]) * wgt);
+              v.y = pack2<BF16>(__uint_as_float(o[8 * e + 2]) * wgt, __uint_as_float(o[8 * e + 3]) * wgt);
+              v.z = pack2<BF16>(__uint_as_float(o[8 * e + 4]) * wgt, __uint_as_float(o[8 * e + 5]) * wgt);
+              v.w = pack2<BF16>(__uint_as_float(o[8 * e + 6]) * wgt, __uint_as_float(o[8 * e + 7]) * wgt);
+              *reinterpret_cast<uint4*>(orow + c * 64 + e * 16) = v;
+            }
+          }
+        }
+      } else {
+        // this split's contribution to the final rows, already weighted: fp32 rows in the (idle) K ring
+        float* part = reinterpret_cast<float*>(sK);
+#pragma unroll 1
+        for (int c = 0; c < kHalf / 32; ++c) {
+          uint32_t o[32];
+          if (n > 0) {
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld_wait();
+          }
+          float4* dst = reinterpret_cast<float4*>(part + row * Cfg::kPartRow + col0 + c * 32);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (n > 0) {
+              v.x = __uint_as_float(o[4 * e + 0]) * wgt;
+              v.y = __uint_as_float(o[4 * e + 1]) * wgt;
+              v.z = __uint_as_float(o[4 * e + 2]) * wgt;
+              v.w = __uint_as_float(o[4 * e + 3]) * wgt;
+            }
+            dst[e] = v;
+          }
+        }
+        fence_proxy_async_smem();        // the rows are read by bulk copies (async proxy) below
       }
-      fence_proxy_async_smem();        // the rows are read by bulk copies (async proxy) below
-      if (row == 0) WE_TRACE(232 + st);
+      if (row == 0) WE_TRACE(234 + wg);
     } else {
       // ------------------------------- workspace path: hand the CTA's partial over through global memory
       float acc[kHalf];
 #pragma unroll
       for (int c = 0; c < kHalf / 32; ++c) {
-        uint32_t oa[32], ob[32];
-        if (has_a) tmem_ld32(oa_addr + c * 32, oa);
-        if (has_b) tmem_ld32(ob_addr + c * 32, ob);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float va = has_a ? __uint_as_float(oa[e]) * w_a : 0.f;
-          const float vb = has_b ? __uint_as_float(ob[e]) * w_b : 0.f;
-          acc[c * 32 + e] = va + vb;
+        uint32_t o[32];
+        if (n > 0) {
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
         }
+#pragma unroll
+        for (int e = 0; e < 32; ++e) acc[c * 32 + e] = n > 0 ? __uint_as_float(o[e]) : 0.f;
       }
       const int unit = (b * p.Hq + h) * p.n_qtiles + qt;
-      const bool in_range = q0 + row < p.T;
-      uint8_t* orow = static_cast<uint8_t*>(p.out) +
-                      2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + col0);
       // Partial result of this split, column-major so that the 128 row-threads store coalesced.
       float* wo = p.ws_o + (static_cast<int64_t>(unit) * p.nsplit + split) * (DH * kBlockM);
       float* wml = p.ws_ml + (static_cast<int64_t>(unit) * p.nsplit + split) * (2 * kBlockM);
 #pragma unroll
       for (int e = 0; e < kHalf; ++e) __stcg(wo + (col0 + e) * kBlockM + row, acc[e]);
-      if (st == 0) {
+      if (wg == 0) {
         __stcg(wml + row, m_cta);
         __stcg(wml + kBlockM + row, l_cta);
       }
       __threadfence();
       named_bar_sync(1, kSoftmaxThreads);
-      if (tid == 0) WE_TRACE(225);
       if (tid == 0) *s_ticket = static_cast<uint32_t>(atomicAdd(p.ws_cnt + unit, 1));
       named_bar_sync(1, kSoftmaxThreads);
-      if (tid == 0) { WE_TRACE(226); WE_TRACE_VAL(229, *s_ticket); }
       if (*s_ticket == static_cast<uint32_t>(p.nsplit - 1)) {
         // Last split to arrive merges all of them, always in split order (deterministic).
         __threadfence();
@@ -693,11 +731,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const float ls = __ldcg(ml0 + s2 * 2 * kBlockM + kBlockM + row);
           const float ms = __ldcg(ml0 + s2 * 2 * kBlockM + row);
           if (!(ls > 0.f)) continue;
-          const float wgt = fast_exp2(ms - m_all);
-          den += ls * wgt;
+          const float w2 = fast_exp2(ms - m_all);
+          den += ls * w2;
           const float* os2 = o0 + static_cast<int64_t>(s2) * (DH * kBlockM) + col0 * kBlockM + row;
 #pragma unroll
-          for (int e = 0; e < kHalf; ++e) acc[e] = fmaf(wgt, __ldcg(os2 + e * kBlockM), acc[e]);
+          for (int e = 0; e < kHalf; ++e) acc[e] = fmaf(w2, __ldcg(os2 + e * kBlockM), acc[e]);
         }
         const float inv = 1.0f / den;
         if (in_range) {
@@ -712,72 +750,45 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         if (tid == 0) p.ws_cnt[unit] = 0;  // leave the counter ready for the next launch
-        if (tid == 0) WE_TRACE(227);
       }
     }
+  } else if (p.cluster_merge && p.nsplit > 1) {
+    // warp 11: takes part in the cluster barrier X of the softmax warps (all threads of the CTA must)
+    cluster_arrive_release();
+    cluster_wait_acquire();
+  }
+  if ((warp == 8 || warp == 9 || warp == 10) && p.cluster_merge && p.nsplit > 1) {
+    cluster_arrive_release();
+    cluster_wait_acquire();           // barrier X for the producer / MMA warps, after their loops
   }
 
   // ------------------------------------------------ merge of the splits through cluster shared memory
   // CTA `split` of the cluster produces rows [r0, r1) of the query tile.  Every CTA pushes, with one bulk
-  // copy per peer, the rows a peer owns from its own partial tile into that peer's receive buffer (the idle
-  // V ring); the owner then reduces its own rows and the received ones, always in split order, so reruns
-  // are bit-identical.  A launch without splits is a cluster of one and only normalises its own rows.
-  if (p.cluster_merge) {
+  // copy per peer, the (already weighted) rows that peer owns into the peer's receive buffer (the idle V
+  // ring); the owner adds its own rows and the received ones in split order, so reruns are bit-identical.
+  if (p.cluster_merge && p.nsplit > 1) {
     const int ns = p.nsplit;
     const int r0 = (kBlockM * split) / ns, r1 = (kBlockM * (split + 1)) / ns;
     const int R = r1 - r0;
     float* part = reinterpret_cast<float*>(sK);
     float* recv = reinterpret_cast<float*>(sV);
     const int slot_floats = R * Cfg::kPartRow;
-    if (tid == 0) WE_TRACE(234);
-    if (ns > 1) {
-      if (tid == 0) mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((ns - 1) * slot_floats * 4));
-      cluster_arrive_release();
-      cluster_wait_acquire();         // every CTA has left its main loop: its V ring may be written
-      if (tid == 0) {
-        WE_TRACE(235);
-        for (int d = 0; d < ns; ++d) {
-          if (d == split) continue;
-          const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
-          const int my_slot = split < d ? split : split - 1;          // my position among d's peers
-          const uint32_t dst = dsmem_addr(smem_u32(sV) + static_cast<uint32_t>(my_slot * (d1 - d0) * Cfg::kPartRow * 4),
-                                          static_cast<uint32_t>(d));
-          const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
-          bulk_copy_to_peer(dst, smem_u32(part + d0 * Cfg::kPartRow), static_cast<uint32_t>((d1 - d0) * Cfg::kPartRow * 4),
-                            bar);
-        }
+    __syncthreads();                  // this CTA's weighted rows are complete
+    if (tid == 0) {
+      WE_TRACE(236);
+      for (int d = 0; d < ns; ++d) {
+        if (d == split) continue;
+        const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
+        const int my_slot = split < d ? split : split - 1;          // my position among d's peers
+        const uint32_t dst = dsmem_addr(smem_u32(sV) + static_cast<uint32_t>(my_slot * (d1 - d0) * Cfg::kPartRow * 4),
+                                        static_cast<uint32_t>(d));
+        const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
+        bulk_copy_to_peer(dst, smem_u32(part + d0 * Cfg::kPartRow), static_cast<uint32_t>((d1 - d0) * Cfg::kPartRow * 4),
+                          bar);
       }
-      mbar_wait(recv_bar, 0, s_abort);   // the rows of all peers have landed
     }
-    if (tid == 0) WE_TRACE(236);
-    // Per (split, row) weight exp2(m - m_row) / l_row, computed once per row by one thread.
-    float* wtab = recv + (ns - 1) * slot_floats;                 // [ns][R], behind the receive slots
-    auto partial_row = [&](int pp, int rl) -> const float* {
-      return pp == split ? part + (r0 + rl) * Cfg::kPartRow
-                         : recv + (pp < split ? pp : pp - 1) * slot_floats + rl * Cfg::kPartRow;
-    };
-#pragma unroll 1
-    for (int rl = tid; rl < R; rl += kAttnThreads) {
-      float m_all = -INFINITY;
-#pragma unroll 1
-      for (int pp = 0; pp < ns; ++pp) {
-        const float* src = partial_row(pp, rl);
-        if (src[DH + 1] > 0.f) m_all = fmaxf(m_all, src[DH]);
-      }
-      float den = 0.f;
-#pragma unroll 1
-      for (int pp = 0; pp < ns; ++pp) {
-        const float* src = partial_row(pp, rl);
-        const float ls = src[DH + 1];
-        const float wgt = ls > 0.f ? fast_exp2(src[DH] - m_all) : 0.f;   // splits without tiles weigh nothing
-        den += ls * wgt;
-        wtab[pp * R + rl] = wgt;
-      }
-      const float inv = 1.0f / den;
-#pragma unroll 1
-      for (int pp = 0; pp < ns; ++pp) wtab[pp * R + rl] *= inv;
-    }
-    __syncthreads();
+    mbar_wait(recv_bar, 0, s_abort);   // the rows of all peers have landed
+    if (tid == 0) WE_TRACE(237);
     // One item = one row x 4 consecutive columns; consecutive lanes take consecutive columns of a row.
     constexpr int kGroups = DH / 4;
     const int items = R * kGroups;
@@ -789,14 +800,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         if (u < ns) {
-          const float wgt = wtab[u * R + rl];
-          if (wgt != 0.f) {                                        // never touch the stale rows of an empty split
-            const float4 v = *reinterpret_cast<const float4*>(partial_row(u, rl) + c0);
-            acc.x = fmaf(wgt, v.x, acc.x);
-            acc.y = fmaf(wgt, v.y, acc.y);
-            acc.z = fmaf(wgt, v.z, acc.z);
-            acc.w = fmaf(wgt, v.w, acc.w);
-          }
+          const float* src = u == split ? part + (r0 + rl) * Cfg::kPartRow
+                                        : recv + (u < split ? u : u - 1) * slot_floats + rl * Cfg::kPartRow;
+          const float4 v = *reinterpret_cast<const float4*>(src + c0);
+          acc.x += v.x;
+          acc.y += v.y;
+          acc.z += v.z;
+          acc.w += v.w;
         }
       }
       const int row = r0 + rl;
@@ -809,11 +819,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         *reinterpret_cast<uint2*>(o) = v2;
       }
     }
-    if (tid == 0) WE_TRACE(237);
-    if (ns > 1) {
-      cluster_arrive_release();
-      cluster_wait_acquire();         // all copies have been consumed: sources and receive buffers may go away
-    }
+    if (tid == 0) WE_TRACE(238);
+    cluster_arrive_release();
+    cluster_wait_acquire();           // all copies have been consumed: sources and receive buffers may go away
   }
 
   // --------------------------------------------------------------- teardown
