@@ -58,9 +58,8 @@ constexpr int kAttnThreads = 384;
 constexpr int kSoftmaxThreads = 256;
 constexpr int kMaxSplits = 32;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0;    // + 128 * (tile & 1)
-constexpr uint32_t kColO = 256;
-constexpr uint32_t kColP = 384;  // + 64 * (tile & 1)
+constexpr uint32_t kColS = 0;    // + 128 * (tile & 1); group g owns columns [64g, 64g+64), P_g its first 32
+constexpr uint32_t kColO = 256;  // + 128 * group
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int DH>
@@ -142,13 +141,19 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// a * wa + b * wb where a term with weight 0 is dropped outright (its value may be stale or non-finite)
+__device__ __forceinline__ float merge2(float a, float wa, float b, float wb) {
+  const float ta = wa != 0.f ? a * wa : 0.f;
+  return wb != 0.f ? fmaf(b, wb, ta) : ta;
+}
+
 __device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // volatile: stays behind the turn barrier
   return y;
 }
 
@@ -250,10 +255,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kStagesV * Cfg::kTileBytes);
   uint64_t* q_full = bars + 0;
   uint64_t* recv_bar = bars + 1;  // incoming partial rows of the split merge
-  uint64_t* s_ready = bars + 2;   // [2] per stream
-  uint64_t* p_ready = bars + 4;   // [2]
-  uint64_t* o_ready = bars + 6;   // one phase per tile: PV(i) complete
-  uint64_t* k_full = bars + 8;                  // [kStagesK]
+  uint64_t* s_ready = bars + 2;   // [tile & 1]
+  uint64_t* p_ready = bars + 4;   // [group][tile & 1]
+  uint64_t* o_ready = bars + 8;   // [group], one phase per tile: PV_g(i) complete
+  uint64_t* o_final = bars + 10;  // single phase: every MMA of the CTA complete
+  uint64_t* k_full = bars + 11;                 // [kStagesK]
   uint64_t* k_empty = k_full + kStagesK;        // [kStagesK]
   uint64_t* v_full = k_empty + kStagesK;        // [kStagesV]
   uint64_t* v_empty = v_full + kStagesV;        // [kStagesV]
@@ -307,9 +313,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(recv_bar, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_ready[s], 1);
-      mbar_init(&p_ready[s], kSoftmaxThreads);
+      mbar_init(&o_ready[s], 1);
     }
-    mbar_init(o_ready, 1);
+    for (int s = 0; s < 4; ++s) mbar_init(&p_ready[s], kBlockM);
+    mbar_init(o_final, 1);
     for (int s = 0; s < kStagesK; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -448,9 +455,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     __syncwarp();
   } else if (warp == 9) {
     if (lane == 0 && n > 0) {
-      const uint32_t q_addr = smem_u32(sQ);
-      const uint32_t k_addr = smem_u32(sK);
-      const uint32_t v_addr = smem_u32(sV);
+      // Low descriptor words of the operand tiles; a step of 16 along K adds a constant.
+      const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16);                       // K-major, 128-byte swizzle
+      const uint32_t k_lo = umma_desc_lo(smem_u32(sK), 16);
+      const uint32_t v_lo = umma_desc_lo(smem_u32(sV), Cfg::kChunkBytes);         // MN-major: LBO = chunk stride
+      constexpr uint32_t kTileStep = Cfg::kTileBytes >> 4;
       mbar_wait(q_full, 0, s_abort);
       // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; into S buffer i & 1.
       auto issue_s = [&](int i) {
@@ -458,12 +467,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_wait(&k_full[sk], (i / kStagesK) & 1, s_abort);
         tc_fence_after();
         const uint32_t d = tmem_base + kColS + 128u * (i & 1);
+        const uint32_t kb = k_lo + sk * kTileStep;
+        umma_ss_lo<0>(d, q_lo, kb, kIdescS);
 #pragma unroll
-        for (int kk = 0; kk < DH / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::kChunkBytes + (kk & 3) * 32;
-          const uint64_t a = umma_desc_sw128(q_addr + off, 16, 1024);
-          const uint64_t bd = umma_desc_sw128(k_addr + sk * Cfg::kTileBytes + off, 16, 1024);
-          umma_ss(d, a, bd, kIdescS, kk > 0 ? 1u : 0u);
+        for (int kk = 1; kk < DH / 16; ++kk) {
+          constexpr uint32_t kChunkStep = Cfg::kChunkBytes >> 4;
+          const uint32_t off = (kk >> 2) * kChunkStep + (kk & 3) * 2;          // 32 bytes per K step
+          umma_ss_lo<1>(d, q_lo + off, kb + off, kIdescS);
         }
         tc_commit(&k_empty[sk]);
         tc_commit(&s_ready[i & 1]);
@@ -471,45 +481,55 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       issue_s(0);
       for (int i = 0; i < n; ++i) {
         const int sv = i % kStagesV;
-        // S(i+1) goes first: its buffer was released when P(i-1) was handed over, and the tensor pipe
-        // computes it while the softmax warps are busy with S(i).
+        const int buf = i & 1;
+        // S(i+1) goes first: its buffer was released when both halves of P(i-1) were consumed, and the
+        // tensor pipe computes it while the softmax warps are busy with S(i).
+        if (i < 8) WE_TRACE(96 + 6 * i);
         if (i + 1 < n) issue_s(i + 1);
-        mbar_wait(&p_ready[i & 1], (i >> 1) & 1, s_abort);
-        if (i < 24) WE_TRACE(144 + 2 * i);
-        mbar_wait(&v_full[sv], (i / kStagesV) & 1, s_abort);
-        if (i < 24) WE_TRACE(145 + 2 * i);
-        tc_fence_after();
-        // O += P(i) V(i) : M=128 queries, N=DH, K=128 keys in steps of 16 (two bf16 of P per TMEM column).
-        const uint32_t d = tmem_base + kColO;
-        const uint32_t a_t = tmem_base + kColP + 64u * (i & 1);
+        if (i < 8) WE_TRACE(97 + 6 * i);
+        // O_g += P_g(i) V_g(i) for the two key halves g of the tile: M=128 queries, N=DH, K=64 keys in
+        // steps of 16.  P_g sits in the first 32 columns of group g's half of S (two bf16 per column).
+        const uint32_t vb = v_lo + sv * kTileStep;
+        const uint32_t acc0 = i > 0 ? 1u : 0u;
 #pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk) {
-          const uint64_t bd = umma_desc_sw128(v_addr + sv * Cfg::kTileBytes + kk * 2048, Cfg::kChunkBytes, 1024);
-          umma_ts(d, a_t + kk * 8, bd, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
+        for (int g = 0; g < 2; ++g) {
+          mbar_wait(&p_ready[g * 2 + buf], (i >> 1) & 1, s_abort);
+          if (i < 8) WE_TRACE(98 + 6 * i + 2 * g);
+          if (g == 0) mbar_wait(&v_full[sv], (i / kStagesV) & 1, s_abort);
+          tc_fence_after();
+          const uint32_t d = tmem_base + kColO + 128u * g;
+          const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)                                          // 16 keys = 2048 bytes of V rows
+            umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
+          tc_commit(&o_ready[g]);
+          if (i < 8) WE_TRACE(99 + 6 * i + 2 * g);
         }
         tc_commit(&v_empty[sv]);
-        tc_commit(o_ready);
       }
+      tc_commit(o_final);
     }
     __syncwarp();
   } else if (warp < 8) {
     // ------------------------------------------------------- softmax warps
-    // Both groups own all 128 rows; group g handles keys [64g, 64g+64) of every tile and, in the epilogue
-    // and in rescales, columns [DH/2 * g, DH/2 * (g+1)) of O.
+    // Both groups own all 128 rows.  Group g handles keys [64g, 64g+64) of every tile as a stream of its own:
+    // own running maximum, own row sum, own accumulator O_g, so the groups never exchange data per tile.
+    // The exponentials of the two groups take turns (a pair of named barriers): while one group keeps the
+    // special-function units busy, the other loads, reduces and stores.
     const int wg = warp >> 2;
     const int row = tid & 127;           // query row within the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     constexpr int kHalf = DH / 2;
     const int col0 = wg * kHalf;
-    const uint32_t o_addr = tmem_base + lane_base + kColO + col0;
+    const uint32_t o_mine = tmem_base + lane_base + kColO + 128u * wg;
     const int slot_base = static_cast<int>(s_slot[0]);
     const bool hide = s_slot[1] != 0;
     float m_run = -INFINITY;  // running row maximum, log2 domain, possibly stale by <= threshold
-    float l_part = 0.f;       // row sum over this group's keys
+    float l_run = 0.f;        // row sum over this group's keys
+    if (wg == 1 && n > 0) named_bar_arrive(3, kSoftmaxThreads);   // group 0 takes the first turn
     for (int i = 0; i < n; ++i) {
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
-      const uint32_t p_addr = tmem_base + lane_base + kColP + 64u * buf + 32u * wg;
       mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
       if (row == 0 && i < 32) WE_TRACE(16 + 4 * i + 2 * wg);
       tc_fence_after();
@@ -539,23 +559,22 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           mx4[2] = fmaxf(mx4[2], __uint_as_float(s[c][e + 2]));
           mx4[3] = fmaxf(mx4[3], __uint_as_float(s[c][e + 3]));
         }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // the other group holds the other 64 keys of the same rows: exchange the half-row maxima
-      s_x[(buf * 2 + wg) * kBlockM + row] = mx;
-      named_bar_sync(1, kSoftmaxThreads);
-      mx = fmaxf(mx, s_x[(buf * 2 + (wg ^ 1)) * kBlockM + row]);
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // A half tile may be fully masked (its visible keys all lie in the other half): keep the maximum finite
+      // so that exp2(-inf - m) stays 0 instead of NaN.
+      const float m_new = fmaxf(fmaxf(m_run, mx * p.scale_log2), -1e30f);
       const bool need = (m_new - m_run) > kRescaleThreshold;  // first tile: inf > threshold
       float alpha = 1.f;
-      const bool raise = __any_sync(0xffffffffu, need);        // same verdict in both groups (same rows, same data)
+      const bool raise = __any_sync(0xffffffffu, need);
       if (raise) {
         alpha = fast_exp2(m_run - m_new);                       // first tile: exp2(-inf) = 0
-        l_part *= alpha;
+        l_run *= alpha;
         m_run = m_new;
       }
       const float neg_m = -m_run;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
+      named_bar_sync(3 + wg, kSoftmaxThreads);                  // my turn on the special-function units
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -566,42 +585,51 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           sum4[(2 * e + 1) & 3] += p1;
           pk[c * 16 + e] = pack2<BF16>(p0, p1);
         }
-      tmem_st32(p_addr, pk);
-      l_part += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (!(wg == 1 && i == n - 1)) named_bar_arrive(4 - wg, kSoftmaxThreads);   // the other group's turn
+      tmem_st32(s_addr, pk);                                    // P over the S columns this thread has consumed
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
       if (i > 0) {
-        // PV(i-1) has long been issued; its completion makes O safe to touch and is awaited every tile so
+        // PV_g(i-1) has long been issued; its completion makes O_g safe to touch and is awaited every tile so
         // that no phase of the barrier is ever skipped.
-        mbar_wait(o_ready, (i - 1) & 1, s_abort);
+        mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
         if (raise) {
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < kHalf / 32; ++c) {
+          for (int c = 0; c < DH / 32; ++c) {
             uint32_t o[32];
-            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld32(o_mine + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st32(o_addr + c * 32, o);
+            tmem_st32(o_mine + c * 32, o);
           }
         }
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_ready[buf]);
+      mbar_arrive(&p_ready[wg * 2 + buf]);
     }
 
     // ---------------------------------------------------------- after the last tile
     if (n > 0) {
-      mbar_wait(o_ready, (n - 1) & 1, s_abort);
+      mbar_wait(o_final, 0, s_abort);   // (the per-tile barriers of the other group were never followed here)
       tc_fence_after();
     }
     if (row == 0) WE_TRACE(224 + wg);
-    // total row sum = sum of the two groups' halves
-    s_x[wg * kBlockM + row] = l_part;
+    // merge the two groups' streams: exchange (m, l); each group then combines one half of the head dim
+    s_x[(wg * 2 + 0) * kBlockM + row] = m_run;
+    s_x[(wg * 2 + 1) * kBlockM + row] = l_run;
     named_bar_sync(1, kSoftmaxThreads);
-    const float l_cta = l_part + s_x[(wg ^ 1) * kBlockM + row];   // 0 when the split got no tile
-    const float m_cta = m_run;                                     // -inf when the split got no tile
+    const float m_oth = s_x[((wg ^ 1) * 2 + 0) * kBlockM + row];
+    const float l_oth = s_x[((wg ^ 1) * 2 + 1) * kBlockM + row];
+    const float m_cta = fmaxf(m_run, m_oth);                       // -inf when the split got no tile
+    const float w_mine = l_run > 0.f ? fast_exp2(m_run - m_cta) : 0.f;
+    const float w_oth = l_oth > 0.f ? fast_exp2(m_oth - m_cta) : 0.f;
+    const float l_cta = l_run * w_mine + l_oth * w_oth;            // 0 when the split got no tile
+    const float w_g0 = wg == 0 ? w_mine : w_oth, w_g1 = wg == 0 ? w_oth : w_mine;
+    const uint32_t o0_addr = tmem_base + lane_base + kColO + col0;   // this thread's column half of O_0
+    const uint32_t o1_addr = o0_addr + 128u;                          // ... and of O_1
     const bool in_range = q0 + row < p.T;
     uint8_t* orow = static_cast<uint8_t*>(p.out) +
                     2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + col0);
@@ -643,19 +671,25 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (row == 0) WE_TRACE(232 + wg);
       if (p.nsplit == 1) {
         // no peers: normalise and store this thread's half row directly
+        const float wa = w_g0 * wgt, wb = w_g1 * wgt;
 #pragma unroll 1
         for (int c = 0; c < kHalf / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld32(o_addr + c * 32, o);
+          uint32_t oa[32], ob[32];
+          tmem_ld32(o0_addr + c * 32, oa);
+          tmem_ld32(o1_addr + c * 32, ob);
           tmem_ld_wait();
           if (in_range) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
+              float f[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                f[k] = merge2(__uint_as_float(oa[8 * e + k]), wa, __uint_as_float(ob[8 * e + k]), wb);
               uint4 v;
-              v.x = pack2<BF16>(__uint_as_float(o[8 * e + 0]) * wgt, __uint_as_float(o[8 * e + 1]) * wgt);
-              v.y = pack2<BF16>(__uint_as_float(o[8 * e + 2]) * wgt, __uint_as_float(o[8 * e + 3]) * wgt);
-              v.z = pack2<BF16>(__uint_as_float(o[8 * e + 4]) * wgt, __uint_as_float(o[8 * e + 5]) * wgt);
-              v.w = pack2<BF16>(__uint_as_float(o[8 * e + 6]) * wgt, __uint_as_float(o[8 * e + 7]) * wgt);
+              v.x = pack2<BF16>(f[0], f[1]);
+              v.y = pack2<BF16>(f[2], f[3]);
+              v.z = pack2<BF16>(f[4], f[5]);
+              v.w = pack2<BF16>(f[6], f[7]);
               *reinterpret_cast<uint4*>(orow + c * 64 + e * 16) = v;
             }
           }
@@ -663,11 +697,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       } else {
         // this split's contribution to the final rows, already weighted: fp32 rows in the (idle) K ring
         float* part = reinterpret_cast<float*>(sK);
+        const float wa = w_g0 * wgt, wb = w_g1 * wgt;
 #pragma unroll 1
         for (int c = 0; c < kHalf / 32; ++c) {
-          uint32_t o[32];
+          uint32_t oa[32], ob[32];
           if (n > 0) {
-            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld32(o0_addr + c * 32, oa);
+            tmem_ld32(o1_addr + c * 32, ob);
             tmem_ld_wait();
           }
           float4* dst = reinterpret_cast<float4*>(part + row * Cfg::kPartRow + col0 + c * 32);
@@ -675,10 +711,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int e = 0; e < 8; ++e) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (n > 0) {
-              v.x = __uint_as_float(o[4 * e + 0]) * wgt;
-              v.y = __uint_as_float(o[4 * e + 1]) * wgt;
-              v.z = __uint_as_float(o[4 * e + 2]) * wgt;
-              v.w = __uint_as_float(o[4 * e + 3]) * wgt;
+              v.x = merge2(__uint_as_float(oa[4 * e + 0]), wa, __uint_as_float(ob[4 * e + 0]), wb);
+              v.y = merge2(__uint_as_float(oa[4 * e + 1]), wa, __uint_as_float(ob[4 * e + 1]), wb);
+              v.z = merge2(__uint_as_float(oa[4 * e + 2]), wa, __uint_as_float(ob[4 * e + 2]), wb);
+              v.w = merge2(__uint_as_float(oa[4 * e + 3]), wa, __uint_as_float(ob[4 * e + 3]), wb);
             }
             dst[e] = v;
           }
@@ -691,13 +727,15 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       float acc[kHalf];
 #pragma unroll
       for (int c = 0; c < kHalf / 32; ++c) {
-        uint32_t o[32];
+        uint32_t oa[32], ob[32];
         if (n > 0) {
-          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld32(o0_addr + c * 32, oa);
+          tmem_ld32(o1_addr + c * 32, ob);
           tmem_ld_wait();
         }
 #pragma unroll
-        for (int e = 0; e < 32; ++e) acc[c * 32 + e] = n > 0 ? __uint_as_float(o[e]) : 0.f;
+        for (int e = 0; e < 32; ++e)
+          acc[c * 32 + e] = n > 0 ? merge2(__uint_as_float(oa[e]), w_g0, __uint_as_float(ob[e]), w_g1) : 0.f;
       }
       const int unit = (b * p.Hq + h) * p.n_qtiles + qt;
       // Partial result of this split, column-major so that the 128 row-threads store coalesced.
