@@ -1,0 +1,89 @@
+"""Full-size configurations on the GPU: parity with the oracle on a subset of rows (the oracle finishes in
+seconds on those) plus size-independent properties of the operation on the whole output."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ring_attn_oracle as oracle
+from tests import helpers
+from tests import gpu_helpers as gh
+from world_engine_b200 import ops
+from world_engine_b200.synthetic import CONFIGS, frame_kv, frame_q, history_frames
+
+pytestmark = pytest.mark.gpu
+
+ROWS = [0, 1, 63, 64, 127, 128, 200, -1]
+
+
+def _fill(cfg):
+    """Replays the frames that determine the cache state at cfg.frame_t on the GPU and in the oracle."""
+    cache = gh.new_gpu_cache(cfg)
+    ocache = helpers.new_oracle_cache(cfg)
+    for f in history_frames(cfg):
+        _, k, v = helpers.step_inputs(cfg, f, 0)
+        ops.kv_append_(cache.kv, cache.written.view(torch.uint8), gh.dev_tensor(cfg, k), gh.dev_tensor(cfg, v),
+                       gh.pos_ids(cfg, f)["t_pos"], cfg.T, cfg.dilation, False)
+        ocache.upsert(np.stack([helpers.to_container(cfg, k), helpers.to_container(cfg, v)], 0), f, False)
+    return cache, ocache
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg4_session", "cfg5"])
+def test_fullsize_step_matches_oracle_on_row_subset_and_keeps_state_exact(name):
+    cfg = CONFIGS[name]
+    cache, ocache = _fill(cfg)
+    t = cfg.frame_t
+    for step, frozen in ((0, True), (1, False)):
+        q, k, v = helpers.step_inputs(cfg, t, step)
+        out = cache.append_and_attend(gh.dev_tensor(cfg, q), gh.dev_tensor(cfg, k), gh.dev_tensor(cfg, v),
+                                      gh.pos_ids(cfg, t), frozen)
+        kv_new = np.stack([helpers.to_container(cfg, k), helpers.to_container(cfg, v)], 0)
+        k_full, v_full, mask = ocache.upsert(kv_new, t, frozen)
+        assert int(mask.sum()) == cfg.visible_keys()
+        assert gh.kv_bytes(cache) == ocache.kv.tobytes(), "cache contents differ"
+        assert np.array_equal(cache.written.cpu().numpy(), ocache.written)
+        rows = sorted({r % cfg.T for r in ROWS})
+        heads = sorted({0, cfg.Hq // 2, cfg.Hq - 1})
+        kf = helpers.from_container(cfg, k_full[:1, [h * cfg.Hkv // cfg.Hq for h in heads]])
+        vf = helpers.from_container(cfg, v_full[:1, [h * cfg.Hkv // cfg.Hq for h in heads]])
+        want = oracle.frame_attention(q[:1][:, heads][:, :, rows], kf, vf, mask)
+        got = out[:1][:, heads][:, :, rows].float().cpu().numpy()
+        mx, mean = helpers.error_stats(got, want)
+        assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"{name} step {step}: max {mx} mean {mean}"
+        assert torch.isfinite(out.float()).all()
+    ops.check_status(torch.device("cuda"))
+
+
+def test_properties_at_full_size():
+    """cfg2 shape: (1) constant V gives that constant; (2) the output is linear in V; (3) the slot a frame sits
+    in does not matter (keys are a set): shifting the whole history by one ring slot leaves the output unchanged
+    up to summation order."""
+    cfg = CONFIGS["cfg2"]
+    cache, _ = _fill(cfg)
+    t = cfg.frame_t
+    q, k, v = helpers.step_inputs(cfg, t, 0)
+    qd, kd, vd = gh.dev_tensor(cfg, q), gh.dev_tensor(cfg, k), gh.dev_tensor(cfg, v)
+    pos = gh.pos_ids(cfg, t)
+    base = cache.append_and_attend(qd, kd, vd, pos, True).float()
+    # (1) convexity: all V rows equal to c  ->  output equals c
+    saved_v = cache.kv[1].clone()
+    cache.kv[1].fill_(0.75)
+    const = cache.append_and_attend(qd, kd, torch.full_like(vd, 0.75), pos, True).float()
+    assert torch.allclose(const, torch.full_like(const, 0.75), atol=4e-3)
+    # (2) linearity in V: out(V) - out(0.5 V) == out(0.5 V)   (0.5 V is exact in bf16)
+    cache.kv[1].copy_(saved_v * 0.5)
+    half = cache.append_and_attend(qd, kd, vd * 0.5, pos, True).float()
+    assert (base - 2 * half).abs().max().item() <= 2e-2 * max(1.0, base.abs().max().item())
+    assert (base - 2 * half).abs().mean().item() <= 1e-3
+    # (3) permutation of ring slots: the same frame data persisted one slot later and queried one frame later
+    #     leaves the same set of visible keys (the hidden slot again holds the oldest frame)
+    cache.kv[1].copy_(saved_v)
+    from dataclasses import replace
+    cfg_b = replace(cfg, frame_t=t + 1)
+    cache_b = gh.new_gpu_cache(cfg_b)
+    for f in history_frames(cfg):
+        _, kf, vf = helpers.step_inputs(cfg, f, 0)
+        ops.kv_append_(cache_b.kv, cache_b.written.view(torch.uint8), gh.dev_tensor(cfg, kf), gh.dev_tensor(cfg, vf),
+                       gh.pos_ids(cfg, f + 1)["t_pos"], cfg.T, cfg.dilation, False)
+    shifted = cache_b.append_and_attend(qd, kd, vd, gh.pos_ids(cfg_b, t + 1), True).float()
+    assert (shifted - base).abs().max().item() <= 8e-3      # only the summation order differs
+    ops.check_status(torch.device("cuda"))

@@ -10,9 +10,10 @@ tensor, raises.
 from ._lib import ABI_VERSION, WeB200Error, load as load_library  # noqa: F401
 from .kv_cache import B200LayerKVCache, B200StaticKVCache  # noqa: F401
 from .attn import B200Attn, patch_Attn_b200  # noqa: F401
+from .sessions import SessionSlab, shard_sessions  # noqa: F401
 from . import ops  # noqa: F401
 
 __all__ = [
     "ABI_VERSION", "WeB200Error", "load_library",
-    "B200LayerKVCache", "B200StaticKVCache", "B200Attn", "patch_Attn_b200", "ops",
+    "B200LayerKVCache", "B200StaticKVCache", "B200Attn", "patch_Attn_b200", "SessionSlab", "shard_sessions", "ops",
 ]

@@ -215,6 +215,21 @@ __device__ __noinline__ uint32_t chunk_visibility(const uint8_t* wr, int key0, i
   return bits;
 }
 
+// slot_of() with a 32-bit fast path (frame counters below 2^31).
+__device__ __forceinline__ void slot_of_fast(int64_t ft, int64_t L, int T, int dilation, int ring_frames, int& slot_base,
+                                             int& hide) {
+  if (static_cast<uint64_t>(ft) < 0x7FFFFFFFull) {
+    const uint32_t t = static_cast<uint32_t>(ft), d = static_cast<uint32_t>(dilation);
+    const uint32_t buckets = static_cast<uint32_t>(ring_frames) / d;
+    slot_base = static_cast<int>((((t + d - 1u) / d) % buckets) * static_cast<uint32_t>(T));
+    hide = (t % d) == 0u;
+  } else {
+    const SlotInfo si = slot_of(ft, L, T, dilation);
+    slot_base = static_cast<int>(si.base);
+    hide = si.write_step;
+  }
+}
+
 // 16 bytes of `written` starting at token 16*v (zeros past the end of the buffer).
 __device__ __forceinline__ uint4 load_written16(const uint8_t* wr, int v, int C) {
   uint4 w = make_uint4(0u, 0u, 0u, 0u);
@@ -305,34 +320,27 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
   const uint4 w_first = load_written16(wr, tid, p.C);
   if (tid == 0) *s_abort = 0;
-  if (warp == 8 && lane == 0) {
-    prefetch_tensormap(&tm_q);
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_v);
-    mbar_init(q_full, 1);
-    mbar_init(recv_bar, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_ready[s], 1);
-      mbar_init(&o_ready[s], 1);
+  if (warp == 8) {
+    // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final, rings
+    constexpr int kNumBars = 11 + 2 * (kStagesK + kStagesV);
+    static_assert(kNumBars <= 32, "one lane per barrier");
+    if (lane < kNumBars) mbar_init(bars + lane, (lane >= 4 && lane < 8) ? kBlockM : 1);
+    if (lane == 0) {
+      prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_v);
     }
-    for (int s = 0; s < 4; ++s) mbar_init(&p_ready[s], kBlockM);
-    mbar_init(o_final, 1);
-    for (int s = 0; s < kStagesK; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
+    __syncwarp();
+    if (lane == 0) {
+      fence_mbar_init();
+      fence_proxy_async_smem();
+      // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
+      mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
+      const int v3[3] = {q0, h, b};
+      for (int ch = 0; ch < Cfg::kChunks; ++ch)
+        tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, v3[p.q_perm[0]], v3[p.q_perm[1]],
+                    v3[p.q_perm[2]]);
     }
-    for (int s = 0; s < kStagesV; ++s) {
-      mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 1);
-    }
-    fence_mbar_init();
-    fence_proxy_async_smem();
-    // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
-    mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
-    const int v3[3] = {q0, h, b};
-    for (int ch = 0; ch < Cfg::kChunks; ++ch)
-      tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, v3[p.q_perm[0]], v3[p.q_perm[1]],
-                  v3[p.q_perm[2]]);
   }
   if (warp == 9) {
     tmem_alloc(s_tmem, kTmemCols);
@@ -349,17 +357,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // memory and the producer warp compacts them.  (The global loads were issued before the set-up barrier.)
   {
     int slot_base, hide_i;
-    if (static_cast<uint64_t>(ft) < 0x7FFFFFFFull) {
-      // same arithmetic as slot_of(), in 32 bits
-      const uint32_t t = static_cast<uint32_t>(ft), d = static_cast<uint32_t>(p.dilation);
-      const uint32_t buckets = static_cast<uint32_t>(p.ring_frames) / d;
-      slot_base = static_cast<int>((((t + d - 1u) / d) % buckets) * static_cast<uint32_t>(p.T));
-      hide_i = (t % d) == 0u;
-    } else {
-      const SlotInfo si = slot_of(ft, p.L, p.T, p.dilation);
-      slot_base = static_cast<int>(si.base);
-      hide_i = si.write_step;
-    }
+    slot_of_fast(ft, p.L, p.T, p.dilation, p.ring_frames, slot_base, hide_i);
     if (tid == 0) {
       s_slot[0] = slot_base;
       s_slot[1] = hide_i;
