@@ -41,6 +41,9 @@ if ROOT not in sys.path:
 
 N_LAYERS = 24
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu captures
+# summarised under profiles/ (bytes); None where no capture exists for that workload.
+NCU_TRAFFIC_BYTES = {"cfg2": 34.8e6, "cfg4": None, "cfg5": None}
 WORKLOAD = ("cfg2: B=1 H=16 Dh=128 T=256, 16-frame ring wrapped (frame_t=27, slot 11), bf16, append included; "
             "one step = 24 distinct layer caches (855 MB > L2, no flush needed)")
 
@@ -182,45 +185,66 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
-    cfg = CONFIGS["cfg2"]
+    from world_engine_b200 import SessionSlab
+    from world_engine_b200.synthetic import scaled
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    if args.workload == "cfg4":
+        # 64 independent sessions (32-frame rings at random wrap offsets) batched in one launch per layer-step
+        cfg = scaled(CONFIGS["cfg4_session"], B=64)
+        n_layers = 2
+        workload = ("cfg4: 64 sessions x (H=16 Dh=128 T=256, 32-frame ring = 8192 keys), random wrap offsets, bf16, "
+                    "append included; one step = 2 distinct session slabs (2 x 4.4 GB > L2)")
+        layers = []
+        for _ in range(n_layers):
+            slab = SessionSlab(cfg.B, cfg.Hkv, cfg.L, cfg.Dh, torch.bfloat16, cfg.T, device=dev)
+            slab._slab.normal_(generator=g)
+            slab._written.fill_(True)
+            slab.frame_t.copy_(32 + torch.randint(0, 10000, (cfg.B,), device=dev, generator=g))
+            layers.append((slab.kv, slab._written.view(torch.uint8), slab.frame_t, 1))
+        cache = None
+    else:
+        cfg = CONFIGS[args.workload]
+        n_layers = N_LAYERS if args.workload == "cfg2" else 4
+        workload = WORKLOAD if args.workload == "cfg2" else (
+            "cfg5: B=4 H=16 Dh=128 T=1024, 16-frame ring wrapped (16384 keys), bf16, append included; "
+            "one step = 4 distinct layer caches (4 x 570 MB > L2)")
 
-    class ModelCfg:   # the reference's config keys that size the cache (src/model/kv_cache.py:161-179)
-        tokens_per_frame = cfg.T
-        local_window = cfg.ring_frames
-        global_window = cfg.ring_frames
-        global_attn_period = 1 << 30
-        global_attn_offset = 1
-        global_pinned_dilation = 1
-        n_heads = cfg.Hq
-        n_kv_heads = cfg.Hkv
-        d_model = cfg.Hq * cfg.Dh
-        n_layers = N_LAYERS
+        class ModelCfg:   # the reference's config keys that size the cache (src/model/kv_cache.py:161-179)
+            tokens_per_frame = cfg.T
+            local_window = cfg.ring_frames
+            global_window = cfg.ring_frames
+            global_attn_period = 1 << 30
+            global_attn_offset = 1
+            global_pinned_dilation = 1
+            n_heads = cfg.Hq
+            n_kv_heads = cfg.Hkv
+            d_model = cfg.Hq * cfg.Dh
 
-    g = torch.Generator(device=dev).manual_seed(cfg.seed + rank)
-    cache = B200StaticKVCache(ModelCfg, batch_size=cfg.B, dtype=torch.bfloat16).to(dev)
-    for layer in cache.layers:
-        layer.kv.normal_(generator=g)
-        layer.written.fill_(True)
-        layer.validate = False
-    cache.set_frozen(True)
-    shape_q = (N_LAYERS, cfg.B, cfg.Hq, cfg.T, cfg.Dh)
-    shape_kv = (N_LAYERS, cfg.B, cfg.Hkv, cfg.T, cfg.Dh)
+        ModelCfg.n_layers = n_layers
+        cache = B200StaticKVCache(ModelCfg, batch_size=cfg.B, dtype=torch.bfloat16).to(dev)
+        t_pos = torch.full((cfg.B, cfg.T), cfg.frame_t, dtype=torch.long, device=dev)
+        layers = []
+        for layer in cache.layers:
+            layer.kv.normal_(generator=g)
+            layer.written.fill_(True)
+            layer.validate = False
+            layers.append((layer.kv, layer.written.view(torch.uint8), t_pos, 0))
+        cache.set_frozen(True)
+        pos = {"t_pos": t_pos}
+    shape_q = (n_layers, cfg.B, cfg.Hq, cfg.T, cfg.Dh)
+    shape_kv = (n_layers, cfg.B, cfg.Hkv, cfg.T, cfg.Dh)
     q = torch.randn(shape_q, device=dev, dtype=torch.bfloat16, generator=g)
     k = torch.randn(shape_kv, device=dev, dtype=torch.bfloat16, generator=g)
     v = torch.randn(shape_kv, device=dev, dtype=torch.bfloat16, generator=g)
     out = torch.empty_like(q)
-    pos = {"t_pos": torch.full((cfg.B, cfg.T), cfg.frame_t, dtype=torch.long, device=dev)}
 
     def forward_layers():
-        for li in range(N_LAYERS):
-            layer = cache.layers[li]
-            ops.append_attend(q[li], k[li], v[li], layer.kv, layer.written.view(torch.uint8), pos["t_pos"],
-                              cfg.T, 1, True, 0.0, out=out[li])
+        for li, (kv, wr, ft, fts) in enumerate(layers):
+            ops.append_attend(q[li], k[li], v[li], kv, wr, ft, cfg.T, 1, True, 0.0, out=out[li], frame_t_stride=fts)
 
     def attention_only():
-        for li in range(N_LAYERS):
-            layer = cache.layers[li]
-            ops.frame_attn(q[li], layer.kv, layer.written.view(torch.uint8), pos["t_pos"], cfg.T, 1, 0.0, out=out[li])
+        for li, (kv, wr, ft, fts) in enumerate(layers):
+            ops.frame_attn(q[li], kv, wr, ft, cfg.T, 1, 0.0, out=out[li], frame_t_stride=fts)
 
     # warm-up outside graphs (allocates the workspace, sets function attributes)
     forward_layers()
@@ -265,13 +289,15 @@ def run_ours(args):
             graph_attn.replay()
         a1.record(stream)
         torch.cuda.synchronize()
-        attn_us = a0.elapsed_time(a1) * 1e3 / (args.steps * N_LAYERS)
+        attn_us = a0.elapsed_time(a1) * 1e3 / (args.steps * n_layers)
     ops.check_status(dev)
 
     if args.profile:
         if rank == 0:
-            print(json.dumps({"profile_run": True, "us_per_layer_step": ms * 1e3 / (N_LAYERS * args.steps),
-                              "attn_us_per_launch": attn_us}))
+            print(json.dumps({"profile_run": True, "workload": args.workload,
+                              "us_per_layer_step": ms * 1e3 / (n_layers * args.steps),
+                              "attn_us_per_launch": attn_us,
+                              "tflops": cfg.flops() / (ms * 1e-3 / (n_layers * args.steps)) / 1e12}))
         if world > 1:
             dist.destroy_process_group()
         return 0
@@ -285,8 +311,12 @@ def run_ours(args):
         dq.copy_(hq, non_blocking=True)
         dk.copy_(hk, non_blocking=True)
         dv.copy_(hv, non_blocking=True)
-        for li in range(N_LAYERS):
-            y = cache.append_and_attend(dq[li], dk[li], dv[li], pos, li)
+        for li in range(n_layers):
+            if cache is not None:     # public API of the layer caches
+                y = cache.append_and_attend(dq[li], dk[li], dv[li], pos, li)
+            else:                     # public API of the session slab
+                kv, wr, ft, fts = layers[li]
+                y = ops.append_attend(dq[li], dk[li], dv[li], kv, wr, ft, cfg.T, 1, True, 0.0, frame_t_stride=fts)
             hout[li].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
         return float(hout[0, 0, 0, 0, 0])
@@ -310,30 +340,37 @@ def run_ours(args):
 
     if rank == 0:
         hbm_peak, tc_peak, peak_kind = measured_peaks()
-        total_layer_steps = world * N_LAYERS * args.steps
+        total_layer_steps = world * n_layers * args.steps
         value = total_layer_steps / (ms * 1e-3)
-        us_per_layer_step = ms * 1e3 / (N_LAYERS * args.steps)
+        us_per_layer_step = ms * 1e3 / (n_layers * args.steps)
         elem = 2
         attn_bytes = cfg.B * (2 * cfg.Hkv * cfg.visible_keys() * cfg.Dh * elem + 2 * cfg.Hq * cfg.T * cfg.Dh * elem)
-        achieved = attn_bytes / (attn_us * 1e-6) / 1e9
+        # the slower of HBM time and tensor time bounds the kernel (measured peaks)
+        t_hbm = attn_bytes / (hbm_peak * 1e9)
+        t_tc = cfg.flops() / (tc_peak * 1e12)
+        if t_tc > t_hbm:
+            roof = {"bound": "tensor", "achieved": cfg.flops() / (attn_us * 1e-6) / 1e12, "peak": tc_peak,
+                    "unit": "TFLOP/s"}
+        else:
+            roof = {"bound": "hbm", "achieved": attn_bytes / (attn_us * 1e-6) / 1e9, "peak": hbm_peak, "unit": "GB/s"}
+        roof.update({"frac": roof["achieved"] / roof["peak"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                     "peak_kind": peak_kind, "kernel": "frame_attn_kernel<128,bf16>", "us_per_launch": attn_us,
+                     "algorithmic_bytes_per_launch": attn_bytes, "flop_per_launch": cfg.flops()})
         cpu = None
         if world == 1:   # reported baseline: rank 0 at N=1 only
-            cpu_med, cpu_times = cpu_layer_step_seconds(cfg, 40)
+            cpu_med, cpu_times = cpu_layer_step_seconds(CONFIGS["cfg2"], 40)
             cpu = {"value": 1.0 / cpu_med, "unit": "layer-steps/s", "cores": host_threads(), "kind": "port",
                    "sample": f"{len(cpu_times)} layer-steps of the cfg2 shape, median (numpy oracle)"}
         line = {
             "metric": "frame-attn layer-steps/s (append + attention)", "value": value, "unit": "layer-steps/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layer_steps_per_step": N_LAYERS, "sessions_per_gpu": 1,
-                       "l2": "inputs larger than L2 (855 MB of cache per step)"},
+            "config": {"workload": workload, "layer_steps_per_step": n_layers, "sessions_per_gpu": cfg.B,
+                       "l2": "inputs larger than L2 (distinct caches cycled within a step)"},
             "us_per_layer_step": us_per_layer_step,
             "tflops": cfg.flops() / (us_per_layer_step * 1e-6) / 1e12,
-            "sessions_frames_per_s": value / (N_LAYERS * 5),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "frame_attn_kernel<128,bf16>", "us_per_launch": attn_us,
-                         "algorithmic_bytes_per_launch": attn_bytes},
+            "sessions_frames_per_s": value * cfg.B / (24 * 5) if args.workload == "cfg4" else value / (24 * 5),
+            "roofline": roof,
             "cpu_baseline": cpu,
             "e2e": {"value": total_layer_steps / (e2e_ms * 1e-3), "unit": "layer-steps/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -352,6 +389,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=["cfg2", "cfg4", "cfg5"], default="cfg2",
+                    help="cfg2 (default, the headline layer-step); cfg4 = 64 sessions with 32-frame rings batched in "
+                         "one launch per layer-step; cfg5 = B=4, 1024 tokens per frame, 16384 keys")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed legs only (skips the end-to-end and CPU-baseline legs): for runs under ncu")
     args = ap.parse_args()
