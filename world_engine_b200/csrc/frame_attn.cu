@@ -218,7 +218,7 @@ __device__ __noinline__ uint32_t chunk_visibility(const uint8_t* wr, int key0, i
 // slot_of() with a 32-bit fast path (frame counters below 2^31).
 __device__ __forceinline__ void slot_of_fast(int64_t ft, int64_t L, int T, int dilation, int ring_frames, int& slot_base,
                                              int& hide) {
-  if (static_cast<uint64_t>(ft) < 0x7FFFFFFFull) {
+  if (static_cast<uint64_t>(ft) < 0x3FFFFFFFull) {
     const uint32_t t = static_cast<uint32_t>(ft), d = static_cast<uint32_t>(dilation);
     const uint32_t buckets = static_cast<uint32_t>(ring_frames) / d;
     slot_base = static_cast<int>((((t + d - 1u) / d) % buckets) * static_cast<uint32_t>(T));
@@ -283,7 +283,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint32_t* s_tmem = s_misc + 0;
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_misc + 1);
   volatile uint32_t* s_nlist = s_misc + 2;
-  uint32_t* s_ticket = s_misc + 3;
+  uint32_t* s_ticket = s_misc + 12;
   volatile int64_t* s_slot = reinterpret_cast<volatile int64_t*>(s_misc + 4);  // [0] base, [1] hide flag
   float* s_ml = reinterpret_cast<float*>(s_misc + 16);                // [stream][m, l][128]
   float* s_x = s_ml;                                                  // [tile & 1][group][128] half-row exchange
@@ -318,8 +318,26 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // ---------------------------------------------------------------- set-up
   // Issue the only global loads of the prologue right away; they are consumed after the set-up barrier.
   const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
-  const uint4 w_first = load_written16(wr, tid, p.C);
   if (tid == 0) *s_abort = 0;
+  // Candidate tiles = physical tiles minus those that lie entirely in the hidden slot (pure arithmetic on
+  // the frame counter).  Split `split` owns candidates [c0, c1); which of them hold a visible key is decided
+  // below from `written`.
+  int slot_base, hide_i;
+  slot_of_fast(ft, p.L, p.T, p.dilation, p.ring_frames, slot_base, hide_i);
+  const int hid_lo = hide_i ? slot_base : 0, hid_hi = hide_i ? slot_base + p.T : 0;   // hidden token range
+  const int first_h = hide_i ? (slot_base + kBlockN - 1) / kBlockN : 0;
+  const int last_h = hide_i ? (slot_base + p.T) / kBlockN : 0;
+  const int count_h = last_h > first_h ? last_h - first_h : 0;
+  const int n_cand = p.ntiles - count_h;
+  const int c0 = static_cast<int>((static_cast<int64_t>(n_cand) * split) / p.nsplit);
+  const int c1 = static_cast<int>((static_cast<int64_t>(n_cand) * (split + 1)) / p.nsplit);
+  const int np = c1 - c0;
+  auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
+  constexpr int kBlind = 2;                       // tiles loaded before their visibility is known
+  const int nblind = np < kBlind ? np : kBlind;
+  // this thread's first 16 tokens of `written` (of its candidate range), in flight during the set-up
+  const int my_j = tid >> 3;
+  const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (tid & 7) : 0x3FFFFFF, p.C);
   if (warp == 8) {
     // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final, rings
     constexpr int kNumBars = 11 + 2 * (kStagesK + kStagesV);
@@ -340,6 +358,22 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int ch = 0; ch < Cfg::kChunks; ++ch)
         tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, v3[p.q_perm[0]], v3[p.q_perm[1]],
                     v3[p.q_perm[2]]);
+      // The first tiles of the range are fetched right away, before it is known whether they hold a visible
+      // key (they almost always do): DRAM latency then overlaps the rest of the prologue.  A tile that the
+      // preceding kernel (the append) may still be writing -- anything reaching into the tail -- waits for it.
+      for (int j = 0; j < nblind; ++j) {
+        const int key0 = phys_tile(c0 + j) * kBlockN;
+        if (key0 + kBlockN > p.L) grid_dependency_wait();
+        const int k3[3] = {key0, kvh, b};
+        mbar_arrive_expect_tx(&k_full[j], Cfg::kTileBytes);
+        for (int ch = 0; ch < Cfg::kChunks; ++ch)
+          tma_load_4d(sK + j * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_k, &k_full[j], ch * 64,
+                      k3[p.kv_perm[0]], k3[p.kv_perm[1]], k3[p.kv_perm[2]]);
+        mbar_arrive_expect_tx(&v_full[j], Cfg::kTileBytes);
+        for (int ch = 0; ch < Cfg::kChunks; ++ch)
+          tma_load_4d(sV + j * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_v, &v_full[j], ch * 64,
+                      k3[p.kv_perm[0]], k3[p.kv_perm[1]], k3[p.kv_perm[2]]);
+      }
     }
   }
   if (warp == 9) {
@@ -353,29 +387,27 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem_base = *s_tmem;
 
   // ------------------------------------------------------ visible-tile list
-  // All threads: 16 tokens each, eight lanes make one 128-key tile; the per-tile counts go to shared
-  // memory and the producer warp compacts them.  (The global loads were issued before the set-up barrier.)
+  // 16 tokens per thread, eight lanes make one 128-key tile; the per-tile counts of the CTA's candidates go
+  // to shared memory and the producer warp compacts them into the list of tiles to walk.
   {
-    int slot_base, hide_i;
-    slot_of_fast(ft, p.L, p.T, p.dilation, p.ring_frames, slot_base, hide_i);
     if (tid == 0) {
       s_slot[0] = slot_base;
       s_slot[1] = hide_i;
     }
-    const int hid_lo = hide_i ? slot_base : 0, hid_hi = hide_i ? slot_base + p.T : 0;  // hidden token range
-    const int nvec = (p.C + 15) >> 4;
-    const int nvec_pad = (nvec + 31) & ~31;  // whole warps take part in the shuffles
+    const int nvec_pad = (np * 8 + 31) & ~31;      // whole warps take part in the shuffles
 #pragma unroll 1
-    for (int v = tid; v < nvec_pad; v += kAttnThreads) {
+    for (int idx = tid; idx < nvec_pad; idx += kAttnThreads) {
+      const int j = idx >> 3;
+      const int v = j < np ? phys_tile(c0 + j) * 8 + (idx & 7) : 0x3FFFFFF;
       uint4 w = w_first;
-      if (v != tid) w = load_written16(wr, v, p.C);
+      if (idx != tid) w = load_written16(wr, v, p.C);
       const int k0 = v * 16;
       // one bit per non-zero byte
       const uint32_t nz0 = __vcmpne4(w.x, 0u) & 0x01010101u, nz1 = __vcmpne4(w.y, 0u) & 0x01010101u;
       const uint32_t nz2 = __vcmpne4(w.z, 0u) & 0x01010101u, nz3 = __vcmpne4(w.w, 0u) & 0x01010101u;
       int cnt = __popc(nz0) + __popc(nz1) + __popc(nz2) + __popc(nz3);
       const int lo = max(k0, hid_lo), hi = min(k0 + 16, hid_hi);
-      if (lo < hi) {
+      if (j < np && lo < hi) {
         if (lo == k0 && hi == k0 + 16) {
           cnt = 0;                                   // the whole vector lies in the hidden slot
         } else {
@@ -386,30 +418,43 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
-      if ((lane & 7) == 0 && (v >> 3) < p.ntiles) s_cnt[v >> 3] = static_cast<uint8_t>(cnt);
+      if ((lane & 7) == 0 && j < np) s_cnt[j] = static_cast<uint8_t>(cnt);
     }
   }
   __syncthreads();
-  int n_list = 0;
+  int n = 0;                 // tiles of this CTA with at least one visible key
+  uint32_t blind_vis = 0;    // bit j: the j-th tile loaded ahead of time turned out visible
   if (warp == 8) {
 #pragma unroll 1
-    for (int base = 0; base < p.ntiles; base += 32) {
+    for (int base = 0; base < np; base += 32) {
       const int j = base + lane;
-      const int c = j < p.ntiles ? s_cnt[j] : 0;
+      const int c = j < np ? s_cnt[j] : 0;
       const unsigned m = __ballot_sync(0xffffffffu, c != 0);
-      if (c != 0) s_list[n_list + __popc(m & ((1u << lane) - 1u))] = static_cast<uint16_t>((j << 1) | (c != kBlockN ? 1 : 0));
-      n_list += __popc(m);
+      if (c != 0)
+        s_list[n + __popc(m & ((1u << lane) - 1u))] =
+            static_cast<uint16_t>((phys_tile(c0 + j) << 1) | (c != kBlockN ? 1 : 0));
+      if (base == 0) blind_vis = m & ((1u << nblind) - 1u);
+      n += __popc(m);
     }
-    if (lane == 0) *s_nlist = static_cast<uint32_t>(n_list);
+    if (lane == 0) {
+      s_nlist[0] = static_cast<uint32_t>(n);
+      s_nlist[1] = blind_vis;
+    }
     __threadfence_block();
     named_bar_arrive(2, kAttnThreads);   // the other warps sleep on this barrier instead of polling
   } else {
     named_bar_sync(2, kAttnThreads);
-    n_list = static_cast<int>(*s_nlist);
+    n = static_cast<int>(s_nlist[0]);
+    blind_vis = s_nlist[1];
   }
-  const int t0 = static_cast<int>((static_cast<int64_t>(n_list) * split) / p.nsplit);
-  const int t1 = static_cast<int>((static_cast<int64_t>(n_list) * (split + 1)) / p.nsplit);
-  const int n = t1 - t0;
+  constexpr int t0 = 0;
+  // Position of the i-th visible tile in the order the tiles were (or will be) loaded: the tiles fetched ahead
+  // of time come first, whether visible or not; every later load is a visible tile.
+  const int n_vis_blind = __popc(blind_vis);
+  auto load_seq = [&](int i) {
+    if (i < n_vis_blind) return (i == 0 && (blind_vis & 1u)) ? 0 : 1;   // kBlind == 2
+    return i + (nblind - n_vis_blind);
+  };
   if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
   // ------------------------------------------------------------------ roles
@@ -421,12 +466,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   if (warp == 8) {
     if (lane == 0) {
-      // K ring: K(i) is issued as soon as S(i - kStagesK) has consumed its stage.
+      // K ring: a tile is issued as soon as the S that used its stage has completed.
       for (int i = 0; i < n; ++i) {
-        const int sk = i % kStagesK;
-        const int key0 = (s_list[t0 + i] >> 1) * kBlockN;
+        const int a = load_seq(i);
+        if (a < nblind) continue;                    // fetched ahead of time
+        const int sk = a % kStagesK;
+        const int key0 = (s_list[i] >> 1) * kBlockN;
         const int v3[3] = {key0, kvh, b};
-        if (i >= kStagesK) mbar_wait(&k_empty[sk], ((i / kStagesK) - 1) & 1, s_abort);
+        if (a >= kStagesK) mbar_wait(&k_empty[sk], ((a / kStagesK) - 1) & 1, s_abort);
         if (i < 32) WE_TRACE(192 + i);
         mbar_arrive_expect_tx(&k_full[sk], Cfg::kTileBytes);
         for (int ch = 0; ch < Cfg::kChunks; ++ch)
@@ -440,10 +487,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (lane == 0) {
       // V ring, on its own thread so that a full V ring never holds back a K load.
       for (int i = 0; i < n; ++i) {
-        const int sv = i % kStagesV;
-        const int key0 = (s_list[t0 + i] >> 1) * kBlockN;
+        const int a = load_seq(i);
+        if (a < nblind) continue;
+        const int sv = a % kStagesV;
+        const int key0 = (s_list[i] >> 1) * kBlockN;
         const int v3[3] = {key0, kvh, b};
-        if (i >= kStagesV) mbar_wait(&v_empty[sv], ((i / kStagesV) - 1) & 1, s_abort);
+        if (a >= kStagesV) mbar_wait(&v_empty[sv], ((a / kStagesV) - 1) & 1, s_abort);
         mbar_arrive_expect_tx(&v_full[sv], Cfg::kTileBytes);
         for (int ch = 0; ch < Cfg::kChunks; ++ch)
           tma_load_4d(sV + sv * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_v, &v_full[sv], ch * 64,
@@ -452,6 +501,17 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     __syncwarp();
   } else if (warp == 9) {
+    if (lane == 0) {
+      // tiles fetched ahead of time that hold no visible key: let them land, then free their stages
+      for (int j = 0; j < nblind; ++j) {
+        if (!((blind_vis >> j) & 1u)) {
+          mbar_wait(&k_full[j], 0, s_abort);
+          mbar_arrive(&k_empty[j]);
+          mbar_wait(&v_full[j], 0, s_abort);
+          mbar_arrive(&v_empty[j]);
+        }
+      }
+    }
     if (lane == 0 && n > 0) {
       // Low descriptor words of the operand tiles; a step of 16 along K adds a constant.
       const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16);                       // K-major, 128-byte swizzle
@@ -461,8 +521,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(q_full, 0, s_abort);
       // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; into S buffer i & 1.
       auto issue_s = [&](int i) {
-        const int sk = i % kStagesK;
-        mbar_wait(&k_full[sk], (i / kStagesK) & 1, s_abort);
+        const int a = load_seq(i);
+        const int sk = a % kStagesK;
+        mbar_wait(&k_full[sk], (a / kStagesK) & 1, s_abort);
         tc_fence_after();
         const uint32_t d = tmem_base + kColS + 128u * (i & 1);
         const uint32_t kb = k_lo + sk * kTileStep;
@@ -478,7 +539,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       };
       issue_s(0);
       for (int i = 0; i < n; ++i) {
-        const int sv = i % kStagesV;
+        const int av = load_seq(i);
+        const int sv = av % kStagesV;
         const int buf = i & 1;
         // S(i+1) goes first: its buffer was released when both halves of P(i-1) were consumed, and the
         // tensor pipe computes it while the softmax warps are busy with S(i).
@@ -493,7 +555,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int g = 0; g < 2; ++g) {
           mbar_wait(&p_ready[g * 2 + buf], (i >> 1) & 1, s_abort);
           if (i < 8) WE_TRACE(98 + 6 * i + 2 * g);
-          if (g == 0) mbar_wait(&v_full[sv], (i / kStagesV) & 1, s_abort);
+          if (g == 0) mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
           tc_fence_after();
           const uint32_t d = tmem_base + kColO + 128u * g;
           const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
@@ -535,6 +597,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_ld32(s_addr, s[0]);
       tmem_ld32(s_addr + 32, s[1]);
       tmem_ld_wait();
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 0);
       const uint32_t entry = s_list[t0 + i];
       if (entry & 1u) {
         // partial tile: mask tokens that are unwritten, hidden, or beyond the buffer
@@ -572,7 +635,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const float neg_m = -m_run;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 1);
       named_bar_sync(3 + wg, kSoftmaxThreads);                  // my turn on the special-function units
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 2);
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
@@ -583,6 +648,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           sum4[(2 * e + 1) & 3] += p1;
           pk[c * 16 + e] = pack2<BF16>(p0, p1);
         }
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 3);
       if (!(wg == 1 && i == n - 1)) named_bar_arrive(4 - wg, kSoftmaxThreads);   // the other group's turn
       tmem_st32(s_addr, pk);                                    // P over the S columns this thread has consumed
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
@@ -590,7 +656,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (i > 0) {
         // PV_g(i-1) has long been issued; its completion makes O_g safe to touch and is awaited every tile so
         // that no phase of the barrier is ever skipped.
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 4);
         mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 5);
         if (raise) {
           tc_fence_after();
 #pragma unroll 1
@@ -605,11 +673,16 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       tmem_st_wait();
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 6);
       tc_fence_before();
       mbar_arrive(&p_ready[wg * 2 + buf]);
+      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 7);
     }
 
     // ---------------------------------------------------------- after the last tile
+    // A kernel queued behind this one with a programmatic dependency (the next layer-step's append) may be
+    // scheduled from here on; it waits for this grid to complete before it touches memory.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (n > 0) {
       mbar_wait(o_final, 0, s_abort);   // (the per-tile barriers of the other group were never followed here)
       tc_fence_after();

@@ -37,8 +37,11 @@ __global__ void __launch_bounds__(kAppendThreads) kv_append_kernel(const AppendP
   __shared__ int64_t s_base;
   __shared__ int s_ring;  // 1 when this call also persists into the ring slot
 
-  // Let a kernel launched with a programmatic dependency on this one (the attention of the same layer-step)
-  // begin its prologue now; it waits for this grid to finish before it reads what is written here.
+  // Programmatic dependent launch, both ways.  This kernel may itself have been started before the kernel
+  // ahead of it in the stream finished: wait for that one first (returns at once otherwise).  Only then let
+  // the kernel behind it (the attention of the same layer-step) begin its prologue: that kernel may rely on
+  // everything older than this append being complete, and it waits for this grid before it reads the cache.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int plane = blockIdx.y / p.B;
   const int b = blockIdx.y - plane * p.B;
@@ -128,10 +131,22 @@ int kv_append_launch(const void* k_new, const int64_t* ks, const void* v_new, co
   const int64_t gx = (per_b + kAppendThreads - 1) / kAppendThreads;
   if (gx > 0x7FFFFFFF || 2 * static_cast<int64_t>(g->B) > 65535) return WE_B200_E_LIMIT;
   dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(2 * g->B));
-  kv_append_kernel<<<grid, kAppendThreads, 0, stream>>>(p);
+  // Launched with programmatic stream serialization: its CTAs may be scheduled while the previous kernel of
+  // the stream drains (they wait for it first thing), which hides the launch latency between layer-steps.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kAppendThreads, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kv_append_kernel, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  const cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? WE_B200_OK : static_cast<int>(e);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const cudaError_t e2 = cudaGetLastError();
+  return e2 == cudaSuccess ? WE_B200_OK : static_cast<int>(e2);
 }
 
 }  // namespace we
