@@ -44,9 +44,20 @@ extern "C" int we_b200_append_attend(const void* q, const int64_t* q_strides_hos
                                      const we_b200_cache_geom* geom_host, int is_frozen, float scale, void* workspace,
                                      size_t workspace_bytes, int32_t* status, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // One launch does both when the tail frame is made of whole 128-key tiles and nobody asked for the
+  // visibility vector: the attention kernel reads the new frame from k_new / v_new and copies it into the
+  // cache on the side.  Otherwise: the append kernel, then the attention kernel (which overlaps its prologue
+  // with the append through programmatic dependent launch).
+  const bool two_byte = geom_host != nullptr && (geom_host->dtype == WE_B200_BF16 || geom_host->dtype == WE_B200_F16);
+  if (two_byte && mask_written == nullptr && geom_host->T % 128 == 0 && geom_host->L % 128 == 0 && k_new && v_new &&
+      kv && written && geom_host->Dh % 8 == 0) {
+    const we::FusedAppend fa = {k_new, k_strides_host, v_new, v_strides_host, kv, written, is_frozen};
+    return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
+                                 workspace, workspace_bytes, status, /*after_append=*/false, &fa, s);
+  }
   const int rc = we::kv_append_launch(k_new, k_strides_host, v_new, v_strides_host, kv, written, mask_written,
                                       frame_t, geom_host, is_frozen, s);
   if (rc != WE_B200_OK) return rc;
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               workspace, workspace_bytes, status, /*after_append=*/true, s);
+                               workspace, workspace_bytes, status, /*after_append=*/true, nullptr, s);
 }

@@ -68,9 +68,20 @@ int kv_append_launch(const void* k_new, const int64_t* ks, const void* v_new, co
                      uint8_t* written, uint8_t* mask_written, const int64_t* frame_t, const we_b200_cache_geom* g,
                      int is_frozen, cudaStream_t stream);
 
+// The append of the same layer-step, when it is to ride along inside the attention launch.
+struct FusedAppend {
+  const void* k_new;
+  const int64_t* ks;   // strides (b, h, t) in elements
+  const void* v_new;
+  const int64_t* vs;
+  void* kv_w;
+  uint8_t* written_w;
+  int is_frozen;
+};
+
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
                       const uint8_t* written, const int64_t* frame_t, const we_b200_cache_geom* g, float scale,
                       void* workspace, size_t workspace_bytes, int32_t* status, bool after_append,
-                      cudaStream_t stream);
+                      const FusedAppend* fused_append, cudaStream_t stream);
 
 }  // namespace we

@@ -103,6 +103,18 @@ struct AttnParams {
   int32_t* ws_cnt;               // [unit]
   int32_t* status;
   int32_t cluster_merge;         // 1: the splits of a query tile form a thread-block cluster and merge through DSMEM
+  // fused append (we_b200_append_attend on tile-aligned caches): the new frame is read from k_new / v_new
+  // instead of the tail, and the CTAs of a kv head share the copy of that head's new rows into the cache
+  int32_t fused;
+  int32_t is_frozen;
+  int32_t kn_perm[3], vn_perm[3];
+  const uint4* k_new;
+  const uint4* v_new;
+  int64_t kn_s[3], vn_s[3];      // strides (b, h, t) of k_new / v_new in 16-byte vectors
+  uint4* kv_w;                   // the cache, writable
+  uint8_t* written_w;
+  int64_t plane_stride_v, batch_stride_v;   // cache strides in 16-byte vectors
+  int32_t vpr;                   // 16-byte vectors per (token, head) row
 };
 
 #ifdef WE_ATTN_DEBUG
@@ -254,7 +266,8 @@ __device__ __forceinline__ uint4 load_written16(const uint8_t* wr, int v, int C)
 template <int DH, bool BF16>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_kn,
+                  const __grid_constant__ CUtensorMap tm_vn, const AttnParams p) {
   using Cfg = AttnCfg<DH>;
   constexpr int kStagesK = Cfg::kStagesK;
   constexpr int kStagesV = Cfg::kStagesV;
@@ -315,6 +328,18 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
 #endif
 
+  // One K or V tile into a ring stage.  With the fused append the tiles of the tail frame come straight from
+  // k_new / v_new (the copy into the cache happens on the side and is never read back in this launch).
+  auto load_kv_tile = [&](bool is_k, uint8_t* dst, uint64_t* bar, int key0) {
+    const bool from_new = p.fused && key0 >= p.L;
+    const CUtensorMap* tm = is_k ? (from_new ? &tm_kn : &tm_k) : (from_new ? &tm_vn : &tm_v);
+    const int32_t* perm = from_new ? (is_k ? p.kn_perm : p.vn_perm) : p.kv_perm;
+    const int c3[3] = {from_new ? key0 - static_cast<int>(p.L) : key0, kvh, b};
+    mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
+    for (int ch = 0; ch < Cfg::kChunks; ++ch)
+      tma_load_4d(dst + ch * Cfg::kChunkBytes, tm, bar, ch * 64, c3[perm[0]], c3[perm[1]], c3[perm[2]]);
+  };
+
   // ---------------------------------------------------------------- set-up
   // Issue the only global loads of the prologue right away; they are consumed after the set-up barrier.
   const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
@@ -364,15 +389,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int j = 0; j < nblind; ++j) {
         const int key0 = phys_tile(c0 + j) * kBlockN;
         if (key0 + kBlockN > p.L) grid_dependency_wait();
-        const int k3[3] = {key0, kvh, b};
-        mbar_arrive_expect_tx(&k_full[j], Cfg::kTileBytes);
-        for (int ch = 0; ch < Cfg::kChunks; ++ch)
-          tma_load_4d(sK + j * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_k, &k_full[j], ch * 64,
-                      k3[p.kv_perm[0]], k3[p.kv_perm[1]], k3[p.kv_perm[2]]);
-        mbar_arrive_expect_tx(&v_full[j], Cfg::kTileBytes);
-        for (int ch = 0; ch < Cfg::kChunks; ++ch)
-          tma_load_4d(sV + j * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_v, &v_full[j], ch * 64,
-                      k3[p.kv_perm[0]], k3[p.kv_perm[1]], k3[p.kv_perm[2]]);
+        load_kv_tile(true, sK + j * Cfg::kTileBytes, &k_full[j], key0);
+        load_kv_tile(false, sV + j * Cfg::kTileBytes, &v_full[j], key0);
       }
     }
   }
@@ -472,13 +490,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (a < nblind) continue;                    // fetched ahead of time
         const int sk = a % kStagesK;
         const int key0 = (s_list[i] >> 1) * kBlockN;
-        const int v3[3] = {key0, kvh, b};
         if (a >= kStagesK) mbar_wait(&k_empty[sk], ((a / kStagesK) - 1) & 1, s_abort);
         if (i < 32) WE_TRACE(192 + i);
-        mbar_arrive_expect_tx(&k_full[sk], Cfg::kTileBytes);
-        for (int ch = 0; ch < Cfg::kChunks; ++ch)
-          tma_load_4d(sK + sk * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_k, &k_full[sk], ch * 64,
-                      v3[p.kv_perm[0]], v3[p.kv_perm[1]], v3[p.kv_perm[2]]);
+        load_kv_tile(true, sK + sk * Cfg::kTileBytes, &k_full[sk], key0);
       }
       if (n == 0) mbar_wait(q_full, 0, s_abort);  // nobody else consumes Q: let the copy land before exit
     }
@@ -491,12 +505,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (a < nblind) continue;
         const int sv = a % kStagesV;
         const int key0 = (s_list[i] >> 1) * kBlockN;
-        const int v3[3] = {key0, kvh, b};
         if (a >= kStagesV) mbar_wait(&v_empty[sv], ((a / kStagesV) - 1) & 1, s_abort);
-        mbar_arrive_expect_tx(&v_full[sv], Cfg::kTileBytes);
-        for (int ch = 0; ch < Cfg::kChunks; ++ch)
-          tma_load_4d(sV + sv * Cfg::kTileBytes + ch * Cfg::kChunkBytes, &tm_v, &v_full[sv], ch * 64,
-                      v3[p.kv_perm[0]], v3[p.kv_perm[1]], v3[p.kv_perm[2]]);
+        load_kv_tile(false, sV + sv * Cfg::kTileBytes, &v_full[sv], key0);
       }
     }
     __syncwarp();
@@ -861,10 +871,56 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (tid == 0) p.ws_cnt[unit] = 0;  // leave the counter ready for the next launch
       }
     }
-  } else if (p.cluster_merge && p.nsplit > 1) {
-    // warp 11: takes part in the cluster barrier X of the softmax warps (all threads of the CTA must)
-    cluster_arrive_release();
-    cluster_wait_acquire();
+  } else {
+    // warp 11: the append.  The CTAs that work on one kv head share the copy of that head's new K and V rows
+    // into the tail slice and, on an unfrozen write step, into the ring slot (LayerKVCache.upsert,
+    // src/model/kv_cache.py:138,147-151); one 16-byte vector per lane and step, 4 steps in flight.
+    if (p.fused) {
+      const int group = p.Hq / p.Hkv;
+      const int ctas = group * p.n_qtiles * p.nsplit;               // CTAs per (batch row, kv head)
+      const int rank = ((h - kvh * group) * p.n_qtiles + qt) * p.nsplit + split;
+      const int ra = (p.T * rank) / ctas, rb = (p.T * (rank + 1)) / ctas;
+      const bool to_ring = !p.is_frozen && hide_i;
+      const int64_t C64 = p.C;
+      const int nvec = (rb - ra) * p.vpr * 2;                       // K rows then V rows
+#pragma unroll 1
+      for (int base = 0; base < nvec; base += 128) {
+        uint4 val[4];
+        int64_t dst_tail[4];
+        int tok[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = base + u * 32 + lane;
+          tok[u] = -1;
+          if (idx < nvec) {
+            const int plane = idx >= (nvec >> 1) ? 1 : 0;
+            const int rem = idx - plane * (nvec >> 1);
+            const int t = ra + rem / p.vpr;
+            const int v = rem - (rem / p.vpr) * p.vpr;
+            const uint4* src = plane ? p.v_new : p.k_new;
+            const int64_t* st = plane ? p.vn_s : p.kn_s;
+            val[u] = src[b * st[0] + kvh * st[1] + t * st[2] + v];
+            dst_tail[u] = plane * p.plane_stride_v + b * p.batch_stride_v + (kvh * C64 + p.L + t) * p.vpr + v;
+            tok[u] = (plane == 0 && v == 0 && kvh == 0) ? t : -2;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (tok[u] != -1) {
+            p.kv_w[dst_tail[u]] = val[u];                                         // tail, always
+            if (to_ring) {
+              p.kv_w[dst_tail[u] + (static_cast<int64_t>(slot_base) - p.L) * p.vpr] = val[u];   // ring slot
+              if (tok[u] >= 0) p.written_w[b * p.written_batch_stride + slot_base + tok[u]] = 1;
+            }
+          }
+        }
+      }
+    }
+    if (p.cluster_merge && p.nsplit > 1) {
+      // takes part in the cluster barrier X of the softmax warps (all threads of the CTA must)
+      cluster_arrive_release();
+      cluster_wait_acquire();
+    }
   }
   if ((warp == 8 || warp == 9 || warp == 10) && p.cluster_merge && p.nsplit > 1) {
     cluster_arrive_release();
@@ -1069,8 +1125,9 @@ static int max_active_clusters(int cluster) {
 }
 
 template <int DH, bool BF16>
-static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, AttnParams p,
-                          dim3 grid, bool overlap_previous_kernel, cudaStream_t stream) {
+static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tkn,
+                          const CUtensorMap& tvn, AttnParams p, dim3 grid, bool overlap_previous_kernel,
+                          cudaStream_t stream) {
   using Cfg = AttnCfg<DH>;
   static bool attr_done[64] = {false};
   int dev = 0;
@@ -1109,7 +1166,7 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
   }
   cfg.attrs = n_attr ? attr : nullptr;
   cfg.numAttrs = n_attr;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, frame_attn_kernel<DH, BF16>, tq, tk, tv, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, frame_attn_kernel<DH, BF16>, tq, tk, tv, tkn, tvn, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (e != cudaSuccess) return static_cast<int>(e);
   const cudaError_t e2 = cudaGetLastError();
@@ -1119,7 +1176,7 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
                       const uint8_t* written, const int64_t* frame_t, const we_b200_cache_geom* g, float scale,
                       void* workspace, size_t workspace_bytes, int32_t* status, bool after_append,
-                      cudaStream_t stream) {
+                      const FusedAppend* fa, cudaStream_t stream) {
   if (!q || !out || !kv || !written || !frame_t) return WE_B200_E_NULL;
   int rc = check_geom(g);
   if (rc != WE_B200_OK) return rc;
@@ -1165,7 +1222,7 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   p.ws_ml = reinterpret_cast<float*>(ws + sp.cnt_bytes);
   p.ws_o = reinterpret_cast<float*>(ws + sp.cnt_bytes + sp.ml_bytes);
   p.status = status;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, tkn, tvn;
   const int64_t kvs[3] = {g->kv_batch_stride, C * g->Dh, static_cast<int64_t>(g->Dh)};
   if ((rc = make_map(&tq, q, g->dtype, g->T, Hq, g->B, g->Dh, qs, p.q_perm)) != WE_B200_OK) return rc;
   if ((rc = make_map(&tk, kv, g->dtype, C, g->Hkv, g->B, g->Dh, kvs, p.kv_perm)) != WE_B200_OK) return rc;
@@ -1174,13 +1231,39 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   if ((rc = make_map(&tv, v_base, g->dtype, C, g->Hkv, g->B, g->Dh, kvs, perm_v)) != WE_B200_OK) return rc;
 
   p.cluster_merge = 0;
+  tkn = tk;
+  tvn = tv;
+  p.fused = 0;
+  p.is_frozen = 0;
+  if (fa != nullptr) {
+    // the append rides along: new rows are read through their own tensor maps and copied by one warp per CTA
+    if (!fa->k_new || !fa->v_new || !fa->kv_w || !fa->written_w) return WE_B200_E_NULL;
+    if ((rc = check_strides(fa->ks, 2)) != WE_B200_OK) return rc;
+    if ((rc = check_strides(fa->vs, 2)) != WE_B200_OK) return rc;
+    if (!aligned16(fa->k_new) || !aligned16(fa->v_new)) return WE_B200_E_ALIGN;
+    if ((rc = make_map(&tkn, fa->k_new, g->dtype, g->T, g->Hkv, g->B, g->Dh, fa->ks, p.kn_perm)) != WE_B200_OK) return rc;
+    if ((rc = make_map(&tvn, fa->v_new, g->dtype, g->T, g->Hkv, g->B, g->Dh, fa->vs, p.vn_perm)) != WE_B200_OK) return rc;
+    p.fused = 1;
+    p.is_frozen = fa->is_frozen ? 1 : 0;
+    p.k_new = static_cast<const uint4*>(fa->k_new);
+    p.v_new = static_cast<const uint4*>(fa->v_new);
+    for (int i = 0; i < 3; ++i) {
+      p.kn_s[i] = fa->ks[i] / 8;
+      p.vn_s[i] = fa->vs[i] / 8;
+    }
+    p.kv_w = static_cast<uint4*>(fa->kv_w);
+    p.written_w = fa->written_w;
+    p.plane_stride_v = g->kv_plane_stride / 8;
+    p.batch_stride_v = g->kv_batch_stride / 8;
+    p.vpr = g->Dh / 8;
+  }
   dim3 grid(static_cast<unsigned>(sp.n_qtiles * sp.nsplit), static_cast<unsigned>(Hq), static_cast<unsigned>(g->B));
   if (g->Dh == 128) {
-    return g->dtype == WE_B200_BF16 ? launch_variant<128, true>(tq, tk, tv, p, grid, after_append, stream)
-                                    : launch_variant<128, false>(tq, tk, tv, p, grid, after_append, stream);
+    return g->dtype == WE_B200_BF16 ? launch_variant<128, true>(tq, tk, tv, tkn, tvn, p, grid, after_append, stream)
+                                    : launch_variant<128, false>(tq, tk, tv, tkn, tvn, p, grid, after_append, stream);
   }
-  return g->dtype == WE_B200_BF16 ? launch_variant<64, true>(tq, tk, tv, p, grid, after_append, stream)
-                                  : launch_variant<64, false>(tq, tk, tv, p, grid, after_append, stream);
+  return g->dtype == WE_B200_BF16 ? launch_variant<64, true>(tq, tk, tv, tkn, tvn, p, grid, after_append, stream)
+                                  : launch_variant<64, false>(tq, tk, tv, tkn, tvn, p, grid, after_append, stream);
 }
 
 }  // namespace we
@@ -1203,7 +1286,7 @@ extern "C" int we_b200_frame_attn(const void* q, const int64_t* q_strides_host, 
                                   const int64_t* frame_t, const we_b200_cache_geom* geom_host, float scale,
                                   void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               workspace, workspace_bytes, status, false, static_cast<cudaStream_t>(stream));
+                               workspace, workspace_bytes, status, false, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------- entry point that allocates nothing
@@ -1253,5 +1336,5 @@ extern "C" int we_b200_frame_attn_static(const void* q, const int64_t* q_strides
   e = cudaMemsetAsync(scratch, 0, sp.cnt_bytes, s);
   if (e != cudaSuccess) return static_cast<int>(e);
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               scratch, we::kStaticScratchBytes, status, false, s);
+                               scratch, we::kStaticScratchBytes, status, false, nullptr, s);
 }
