@@ -111,6 +111,7 @@ def cpu_layer_step_seconds(cfg, repeats: int):
     """Times the oracle's layer-step (upsert + attention) on host cores.  Returns median seconds per layer-step."""
     import numpy as np
     from oracle import ring_attn_oracle as oracle   # CPU baseline leg: the one place bench.py may use oracle/
+    use_all_host_threads()
     rng = np.random.default_rng(cfg.seed)
     cache = oracle.OracleLayerKVCache(cfg.B, cfg.Hkv, cfg.L, cfg.Dh, np.uint16, cfg.T, cfg.dilation)
     cache.kv[...] = oracle.f32_to_bf16_bits(rng.standard_normal(cache.kv.shape, dtype=np.float32))
@@ -131,6 +132,18 @@ def host_threads() -> int:
         return len(os.sched_getaffinity(0))
     except Exception:
         return os.cpu_count() or 1
+
+
+def use_all_host_threads() -> int:
+    """The CPU legs use every host core the process may run on, whatever OMP_NUM_THREADS the launcher set
+    (torchrun exports OMP_NUM_THREADS=1).  Returns the thread count in effect."""
+    n = host_threads()
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=n)
+    except Exception:
+        pass
+    return n
 
 
 def run_reference(args):

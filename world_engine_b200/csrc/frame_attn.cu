@@ -120,6 +120,7 @@ struct AttnParams {
 #ifdef WE_ATTN_DEBUG
 // Debug builds only: a per-CTA timeline (SM cycles since the CTA started) written to a caller-provided buffer.
 __device__ uint32_t* g_trace = nullptr;
+__device__ int g_mode = 0;   // experiments: bit 0 = the MMA issuer does not wait for P (results are garbage)
 __device__ __forceinline__ long long trace_clock() {
   long long t;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
@@ -165,7 +166,7 @@ __device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // volatile: stays behind the turn barrier
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -492,6 +493,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int key0 = (s_list[i] >> 1) * kBlockN;
         if (a >= kStagesK) mbar_wait(&k_empty[sk], ((a / kStagesK) - 1) & 1, s_abort);
         if (i < 32) WE_TRACE(192 + i);
+#ifdef WE_ATTN_DEBUG
+        if (g_mode & 4) {   // experiment: no copy, the stage keeps what it held
+          mbar_arrive(&k_full[sk]);
+          continue;
+        }
+#endif
         load_kv_tile(true, sK + sk * Cfg::kTileBytes, &k_full[sk], key0);
       }
       if (n == 0) mbar_wait(q_full, 0, s_abort);  // nobody else consumes Q: let the copy land before exit
@@ -506,6 +513,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int sv = a % kStagesV;
         const int key0 = (s_list[i] >> 1) * kBlockN;
         if (a >= kStagesV) mbar_wait(&v_empty[sv], ((a / kStagesV) - 1) & 1, s_abort);
+#ifdef WE_ATTN_DEBUG
+        if (g_mode & 4) {
+          mbar_arrive(&v_full[sv]);
+          continue;
+        }
+#endif
         load_kv_tile(false, sV + sv * Cfg::kTileBytes, &v_full[sv], key0);
       }
     }
@@ -563,6 +576,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t acc0 = i > 0 ? 1u : 0u;
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
+#ifdef WE_ATTN_DEBUG
+          if (!(g_mode & 1))
+#endif
           mbar_wait(&p_ready[g * 2 + buf], (i >> 1) & 1, s_abort);
           if (i < 8) WE_TRACE(98 + 6 * i + 2 * g);
           if (g == 0) mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
@@ -584,8 +600,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // ------------------------------------------------------- softmax warps
     // Both groups own all 128 rows.  Group g handles keys [64g, 64g+64) of every tile as a stream of its own:
     // own running maximum, own row sum, own accumulator O_g, so the groups never exchange data per tile.
-    // The exponentials of the two groups take turns (a pair of named barriers): while one group keeps the
-    // special-function units busy, the other loads, reduces and stores.
     const int wg = warp >> 2;
     const int row = tid & 127;           // query row within the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -596,12 +610,18 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const bool hide = s_slot[1] != 0;
     float m_run = -INFINITY;  // running row maximum, log2 domain, possibly stale by <= threshold
     float l_run = 0.f;        // row sum over this group's keys
-    if (wg == 1 && n > 0) named_bar_arrive(3, kSoftmaxThreads);   // group 0 takes the first turn
     for (int i = 0; i < n; ++i) {
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
       mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
       if (row == 0 && i < 32) WE_TRACE(16 + 4 * i + 2 * wg);
+#ifdef WE_ATTN_DEBUG
+      if (g_mode & 2) {   // experiment: no softmax work at all, only the hand-over
+        if (i > 0) mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
+        mbar_arrive(&p_ready[wg * 2 + buf]);
+        continue;
+      }
+#endif
       tc_fence_after();
       uint32_t s[2][32];
       tmem_ld32(s_addr, s[0]);
@@ -646,7 +666,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
       if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 1);
-      named_bar_sync(3 + wg, kSoftmaxThreads);                  // my turn on the special-function units
       if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 2);
 #pragma unroll
       for (int c = 0; c < 2; ++c)
@@ -659,7 +678,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           pk[c * 16 + e] = pack2<BF16>(p0, p1);
         }
       if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 3);
-      if (!(wg == 1 && i == n - 1)) named_bar_arrive(4 - wg, kSoftmaxThreads);   // the other group's turn
       tmem_st32(s_addr, pk);                                    // P over the S columns this thread has consumed
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
@@ -1269,6 +1287,9 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
 }  // namespace we
 
 #ifdef WE_ATTN_DEBUG
+extern "C" __attribute__((visibility("default"))) int we_b200_debug_mode(int mode) {
+  return static_cast<int>(cudaMemcpyToSymbol(we::g_mode, &mode, sizeof(mode)));
+}
 // Buffer of 64 x 256 uint32 for the per-CTA timeline (null switches tracing off).
 extern "C" __attribute__((visibility("default"))) int we_b200_debug_trace(uint32_t* buf) {
   return static_cast<int>(cudaMemcpyToSymbol(we::g_trace, &buf, sizeof(buf)));
