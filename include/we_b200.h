@@ -132,10 +132,13 @@ WE_B200_API int we_b200_block_mask(const uint8_t* mask_written, int64_t C, int32
                        void* stream);
 
 /*
- * Bytes of zero-initialised workspace we_b200_frame_attn needs for this
- * shape on the current device (split-KV partials + arrival counters).  The
- * kernel leaves the counters at zero again, so one allocation zeroed once
- * serves every later call of the same or a smaller shape.
+ * Bytes of zero-initialised workspace we_b200_frame_attn may need for this
+ * shape on the current device (split-KV partials + arrival counters).  It is
+ * only touched, and only then required, when the key splits of a query tile
+ * cannot merge through cluster shared memory (splits that merge that way need
+ * no workspace and the pointer may be null).  The kernel leaves the counters
+ * at zero again, so one allocation zeroed once serves every later call of
+ * the same or a smaller shape.
  */
 WE_B200_API size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh, int64_t L);
 
@@ -179,8 +182,9 @@ WE_B200_API int we_b200_append_attend(const void* q, const int64_t* q_strides_ho
  * up front, a plug-in that may only use the buffers it is handed -- and therefore cannot supply the
  * split-KV workspace.  Same arguments and results as we_b200_frame_attn minus the workspace: the scratch
  * lives in a 12 MiB array inside the library image (held by every GPU that loads the library until the
- * process ends).  Shapes whose split-KV plan needs more return WE_B200_E_STATIC_SCRATCH and launch
- * nothing; we_b200_attn_workspace_bytes tells the need in advance.  The call itself performs no
+ * process ends).  It is touched only when the splits of a query tile cannot merge through cluster shared
+ * memory; shapes that then need more than the array holds return WE_B200_E_STATIC_SCRATCH and launch
+ * nothing (we_b200_attn_workspace_bytes tells the need in advance).  The call itself performs no
  * cudaMalloc / cudaFree and calls no allocating routine; inputs, output and status word are still the
  * caller's buffers.  The first call on each device looks up the array's device address (that device
  * must be current) -- make that first call before any stream capture begins.  All calls share the one

@@ -77,7 +77,10 @@ def test_attention_rejects_bad_arguments(lib):
     assert call(_geom(dtype=_lib.F32)) == -4                         # attention is bf16 / f16 only
     assert call(_geom(Dh=96, kv_plane_stride=4 * 320 * 96, kv_batch_stride=4 * 320 * 96)) == -4
     assert call(_geom(), Hq=6) == -3                                 # Hq % Hkv != 0
-    assert call(_geom(), ws=None, ws_bytes=0) == -5                  # split-KV needs a workspace
+    # a long ring is split over several CTAs; where they cannot merge through cluster shared memory (no device
+    # here), the split needs the caller's workspace
+    long_ring = dict(L=64 * 64, kv_plane_stride=4 * 65 * 64 * 64, kv_batch_stride=4 * 65 * 64 * 64)
+    assert call(_geom(**long_ring), ws=None, ws_bytes=0) == -5
     assert call(_geom(L=64 * 4096, kv_plane_stride=4 * 64 * 4097 * 64, kv_batch_stride=4 * 64 * 4097 * 64)) == -7
 
 

@@ -14,8 +14,9 @@ pytestmark = pytest.mark.gpu
 
 
 def test_no_alloc_entry_point_matches_the_workspace_entry_point_twice():
-    # 2 rows x 4 heads x 2 query tiles = 16 units on a 148-SM part -> the KV tiles are split over
-    # several CTAs, so the scratch array (partials + arrival counters) is really used.
+    # 2 rows x 4 heads x 2 query tiles = 16 units on a 148-SM part -> the KV tiles are split over several
+    # CTAs.  Their partial results merge through cluster shared memory where the device can schedule such
+    # clusters and through the built-in scratch array otherwise; either way nothing is allocated.
     cfg = StepConfig("noalloc", 2, 4, 4, 128, 256, 3, 1, 4, "bf16", 31337)
     cache = gh.new_gpu_cache(cfg)
     ocache = helpers.new_oracle_cache(cfg)

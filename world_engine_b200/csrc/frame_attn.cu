@@ -56,7 +56,6 @@ constexpr int kBlockN = 128;    // keys per tile
 constexpr int kMaxTiles = 1024; // capacity limit: 131072 tokens per (row, head)
 constexpr int kAttnThreads = 384;
 constexpr int kSoftmaxThreads = 256;
-constexpr int kMaxSplits = 32;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;    // + 128 * (tile & 1); group g owns columns [64g, 64g+64), P_g its first 32
 constexpr uint32_t kColO = 256;  // + 128 * group
@@ -173,6 +172,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ void cluster_arrive_release() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -191,6 +193,45 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uin
           dst_cluster_addr),
       "r"(src_cta_addr), "r"(bytes), "r"(bar_cluster_addr)
       : "memory");
+}
+// Arrive (count 1) on an mbarrier in a peer CTA's shared memory.  Relaxed: a release fence at cluster scope
+// costs about half a microsecond, so callers that publish data issue ONE fence_cluster() before their arrivals.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+// Bounded wait with acquire at cluster scope, for barriers that peer CTAs arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t it = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++it & 63u) == 0u) {
+      if (*abort_word != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+  }
+}
+// Asynchronous store of two floats into a peer CTA's shared memory; the 8 bytes are signalled on the peer's
+// mbarrier as transaction bytes, so the data is visible to whoever sees that barrier phase complete.
+__device__ __forceinline__ void st_async_f32x2(uint32_t dst_cluster_addr, float a, float b, uint32_t bar_cluster_addr) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(
+                   dst_cluster_addr),
+               "f"(a), "f"(b), "r"(bar_cluster_addr)
+               : "memory");
 }
 __device__ __forceinline__ void st_dsmem_f32x2(uint32_t addr, float a, float b) {
   asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
@@ -288,7 +329,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* p_ready = bars + 4;   // [group][tile & 1]
   uint64_t* o_ready = bars + 8;   // [group], one phase per tile: PV_g(i) complete
   uint64_t* o_final = bars + 10;  // single phase: every MMA of the CTA complete
-  uint64_t* k_full = bars + 11;                 // [kStagesK]
+  uint64_t* ml_bar = bars + 11;   // peers: "my main loop is over and my (m, l) rows are in your table"
+  uint64_t* ack_bar = bars + 12;  // peers: "the rows you pushed to me have landed"
+  uint64_t* k_full = bars + 13;                 // [kStagesK]
   uint64_t* k_empty = k_full + kStagesK;        // [kStagesK]
   uint64_t* v_full = k_empty + kStagesK;        // [kStagesV]
   uint64_t* v_empty = v_full + kStagesV;        // [kStagesV]
@@ -365,10 +408,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int my_j = tid >> 3;
   const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (tid & 7) : 0x3FFFFFF, p.C);
   if (warp == 8) {
-    // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final, rings
-    constexpr int kNumBars = 11 + 2 * (kStagesK + kStagesV);
+    // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final
+    // [11] ml_bar [12] ack_bar, then the rings
+    constexpr int kNumBars = 13 + 2 * (kStagesK + kStagesV);
     static_assert(kNumBars <= 32, "one lane per barrier");
-    if (lane < kNumBars) mbar_init(bars + lane, (lane >= 4 && lane < 8) ? kBlockM : 1);
+    if (lane < kNumBars) {
+      const int peers = p.nsplit > 1 ? p.nsplit - 1 : 1;
+      mbar_init(bars + lane, (lane >= 4 && lane < 8) ? kBlockM : (lane == 12 ? peers : 1));
+    }
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
@@ -378,6 +425,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (lane == 0) {
       fence_mbar_init();
       fence_proxy_async_smem();
+      if (p.cluster_merge && p.nsplit > 1) {
+        // bytes the peers will send to this CTA at the end: their (m, l) pairs and the weighted rows it owns
+        const int rows_mine = (kBlockM * (split + 1)) / p.nsplit - (kBlockM * split) / p.nsplit;
+        mbar_arrive_expect_tx(ml_bar, static_cast<uint32_t>((p.nsplit - 1) * kBlockM * 8));
+        mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRow * 4));
+      }
       // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
       mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
       const int v3[3] = {q0, h, b};
@@ -402,6 +455,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Split-phase cluster barrier: "my barriers are initialised" now, awaited much later, right before the
+  // first access to a peer's shared memory.
+  // (relaxed: the barrier initialisation was already published by fence.mbarrier_init.release.cluster)
+  if (p.cluster_merge && p.nsplit > 1) cluster_arrive_relaxed();
   if (tid == 0) WE_TRACE(1);
   const uint32_t tmem_base = *s_tmem;
 
@@ -738,21 +795,21 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (p.nsplit == 1) {
         wgt = 1.0f / l_cta;
       } else {
-        // announce the bytes the peers will push into this CTA's receive buffer (before any of them can start)
-        if (tid == 0) {
-          const int rows_mine = (kBlockM * (split + 1)) / p.nsplit - (kBlockM * split) / p.nsplit;
-          mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRow * 4));
-        }
-        // every CTA of the cluster learns every split's (m, l): group 0 stores its rows' pair into all peers
+        cluster_wait_acquire();       // every CTA of the cluster has initialised its barriers (long ago)
+        // every CTA of the cluster learns every split's (m, l): group 0 sends its rows' pair to all peers as
+        // asynchronous stores that complete on the peer's barrier (no fence, no extra arrival)
         if (wg == 0) {
           const uint32_t mine = smem_u32(s_mltab + (split * kBlockM + row) * 2);
-          for (int d = 0; d < p.nsplit; ++d) {
-            const uint32_t dst = dsmem_addr(mine, static_cast<uint32_t>(d));
-            st_dsmem_f32x2(dst, m_cta, l_cta);
-          }
+          const uint32_t bar = smem_u32(ml_bar);
+          for (int d = 0; d < p.nsplit; ++d)
+            if (d != split)
+              st_async_f32x2(dsmem_addr(mine, static_cast<uint32_t>(d)), m_cta, l_cta,
+                             dsmem_addr(bar, static_cast<uint32_t>(d)));
         }
-        cluster_arrive_release();
-        cluster_wait_acquire();       // X: all main loops are over (V rings are free) and all pairs are in place
+        s_mltab[(split * kBlockM + row) * 2 + 0] = m_cta;     // own pair (both groups write the same values)
+        s_mltab[(split * kBlockM + row) * 2 + 1] = l_cta;
+        // once all peers' pairs are here their main loops are over, so their V rings may be written
+        mbar_wait_cluster(ml_bar, 0, s_abort);
         float m_all = -INFINITY;
 #pragma unroll 1
         for (int s2 = 0; s2 < p.nsplit; ++s2) {
@@ -934,15 +991,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
     }
-    if (p.cluster_merge && p.nsplit > 1) {
-      // takes part in the cluster barrier X of the softmax warps (all threads of the CTA must)
-      cluster_arrive_release();
-      cluster_wait_acquire();
-    }
-  }
-  if ((warp == 8 || warp == 9 || warp == 10) && p.cluster_merge && p.nsplit > 1) {
-    cluster_arrive_release();
-    cluster_wait_acquire();           // barrier X for the producer / MMA warps, after their loops
   }
 
   // ------------------------------------------------ merge of the splits through cluster shared memory
@@ -971,7 +1019,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
     }
     mbar_wait(recv_bar, 0, s_abort);   // the rows of all peers have landed
-    if (tid == 0) WE_TRACE(237);
+    if (tid == 0) {
+      WE_TRACE(237);
+      // acknowledge to every sender: its staging buffer is no longer read
+      for (int d = 0; d < ns; ++d)
+        if (d != split) mbar_arrive_remote(dsmem_addr(smem_u32(ack_bar), static_cast<uint32_t>(d)));
+    }
     // One item = one row x 4 consecutive columns; consecutive lanes take consecutive columns of a row.
     constexpr int kGroups = DH / 4;
     const int items = R * kGroups;
@@ -1003,8 +1056,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
     }
     if (tid == 0) WE_TRACE(238);
-    cluster_arrive_release();
-    cluster_wait_acquire();           // all copies have been consumed: sources and receive buffers may go away
+    // This CTA may leave once every peer has acknowledged the rows pushed to it; nothing else of this CTA is
+    // touched by a peer after that (their pairs and rows arrived before this CTA summed).
+    mbar_wait_cluster(ack_bar, 0, s_abort);
   }
 
   // --------------------------------------------------------------- teardown
@@ -1098,11 +1152,21 @@ static SplitPlan plan_splits(int B, int Hq, int T, int Dh, int64_t L) {
   s.n_qtiles = (T + kBlockM - 1) / kBlockM;
   s.units = B * Hq * s.n_qtiles;
   s.ntiles = static_cast<int>((L + T + kBlockN - 1) / kBlockN);
+  // Split count: a power of two up to 8 (one thread-block cluster), chosen by a small cost model:
+  // waves of CTAs x (key tiles per CTA + fixed per-CTA cost in tile units: prologue, epilogue, merge).
   const int sms = sm_count();
-  int ns = s.units >= sms ? 1 : sms / s.units;
-  if (ns > s.ntiles) ns = s.ntiles;
-  if (ns > kMaxSplits) ns = kMaxSplits;
-  if (ns < 1) ns = 1;
+  int ns = 1;
+  double best = 0.0;
+  for (int cand = 1; cand <= 8 && cand <= s.ntiles; cand *= 2) {
+    const long long ctas = static_cast<long long>(s.units) * cand;
+    const double waves = static_cast<double>((ctas + sms - 1) / sms);
+    const double tiles = static_cast<double>((s.ntiles + cand - 1) / cand);
+    const double cost = waves * (tiles + (cand == 1 ? 6.0 : 10.0));
+    if (cand == 1 || cost < best * 0.98) {   // a finer split must win by a margin
+      best = cost;
+      ns = cand;
+    }
+  }
   s.nsplit = ns;
   s.o_bytes = ns > 1 ? static_cast<size_t>(s.units) * ns * Dh * kBlockM * sizeof(float) : 0;
   s.ml_bytes = ns > 1 ? static_cast<size_t>(s.units) * ns * 2 * kBlockM * sizeof(float) : 0;
@@ -1142,6 +1206,23 @@ static int max_active_clusters(int cluster) {
   return cached[dev][cluster];
 }
 
+// Can the splits of a query tile merge through cluster shared memory for this kernel variant?
+static bool cluster_merge_available(int Dh, int dtype, int nsplit) {
+  if (nsplit == 1) return true;
+  if (nsplit > 8) return false;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  // the occupancy query needs the opt-in shared-memory size set first
+  auto prep = [&](auto kernel, int smem) {
+    static_cast<void>(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  };
+  if (Dh == 128 && dtype == WE_B200_BF16) { prep(frame_attn_kernel<128, true>, AttnCfg<128>::kSmemBytes); return max_active_clusters<128, true>(nsplit) >= 1; }
+  if (Dh == 128) { prep(frame_attn_kernel<128, false>, AttnCfg<128>::kSmemBytes); return max_active_clusters<128, false>(nsplit) >= 1; }
+  if (dtype == WE_B200_BF16) { prep(frame_attn_kernel<64, true>, AttnCfg<64>::kSmemBytes); return max_active_clusters<64, true>(nsplit) >= 1; }
+  prep(frame_attn_kernel<64, false>, AttnCfg<64>::kSmemBytes);
+  return max_active_clusters<64, false>(nsplit) >= 1;
+}
+
 template <int DH, bool BF16>
 static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tkn,
                           const CUtensorMap& tvn, AttnParams p, dim3 grid, bool overlap_previous_kernel,
@@ -1156,11 +1237,7 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_done[dev] = true;
   }
-  // Splits of one query tile merge through cluster shared memory when they fit a portable cluster and all
-  // clusters of the launch can be resident at once; otherwise through the caller's workspace.
-  const int units = static_cast<int>(grid.x / static_cast<unsigned>(p.nsplit)) * static_cast<int>(grid.y * grid.z);
-  p.cluster_merge = 0;
-  if (p.nsplit == 1 || (p.nsplit <= 8 && max_active_clusters<DH, BF16>(p.nsplit) >= units)) p.cluster_merge = 1;
+  // p.cluster_merge was decided by the caller (cluster_merge_available)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kAttnThreads, 1, 1);
@@ -1211,8 +1288,11 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   if (g->B > 65535 || Hq > 65535) return WE_B200_E_LIMIT;
 
   const SplitPlan sp = plan_splits(g->B, Hq, g->T, g->Dh, g->L);
+  // Splits of one query tile merge through cluster shared memory whenever a cluster of that size can be
+  // scheduled at all (the CTAs of one cluster are always co-resident); only otherwise through the workspace.
+  const bool cluster_ok = cluster_merge_available(g->Dh, g->dtype, sp.nsplit);
   const size_t need = sp.o_bytes + sp.ml_bytes + sp.cnt_bytes;
-  if (sp.nsplit > 1) {
+  if (!cluster_ok) {
     if (workspace == nullptr || workspace_bytes < need) return WE_B200_E_WORKSPACE;
     if (!aligned16(workspace)) return WE_B200_E_ALIGN;
   }
@@ -1248,7 +1328,7 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   const uint8_t* v_base = static_cast<const uint8_t*>(kv) + 2 * g->kv_plane_stride;
   if ((rc = make_map(&tv, v_base, g->dtype, C, g->Hkv, g->B, g->Dh, kvs, perm_v)) != WE_B200_OK) return rc;
 
-  p.cluster_merge = 0;
+  p.cluster_merge = cluster_ok ? 1 : 0;
   tkn = tk;
   tvn = tv;
   p.fused = 0;
@@ -1350,7 +1430,10 @@ extern "C" int we_b200_frame_attn_static(const void* q, const int64_t* q_strides
   if (geom_host == nullptr) return WE_B200_E_NULL;
   if (geom_host->B < 1 || Hq < 1 || geom_host->T < 1 || geom_host->Dh < 1 || geom_host->L < 1) return WE_B200_E_SHAPE;
   const we::SplitPlan sp = we::plan_splits(geom_host->B, Hq, geom_host->T, geom_host->Dh, geom_host->L);
-  if (sp.o_bytes + sp.ml_bytes + sp.cnt_bytes > we::kStaticScratchBytes) return WE_B200_E_STATIC_SCRATCH;
+  if (sp.cnt_bytes > we::kStaticScratchBytes) return WE_B200_E_STATIC_SCRATCH;
+  if (sp.o_bytes + sp.ml_bytes + sp.cnt_bytes > we::kStaticScratchBytes &&
+      !we::cluster_merge_available(geom_host->Dh, geom_host->dtype, sp.nsplit))
+    return WE_B200_E_STATIC_SCRATCH;   // the splits would have to merge through more scratch than the array holds
   // The array keeps whatever the previous call left.  Only the arrival counters must start at zero (the
   // kernel restores them, but a call that was cut short may not have): clear them on the caller's stream.
   cudaStream_t s = static_cast<cudaStream_t>(stream);
