@@ -5,40 +5,45 @@
 // write step, plus the tail frame (LayerKVCache.upsert's mask,
 // src/model/kv_cache.py:141-144, fed to flex_attention at
 // src/model/attn.py:116).  Keys are consumed where they lie: the physical
-// buffer [0, L+T) is cut into 128-key tiles, each CTA builds the list of
-// tiles that hold a visible key from `written` and the device-resident frame
-// counter, and walks its share of that list.  Ring wrap-around therefore is
-// only "which tiles are listed"; nothing is gathered or copied.
+// buffer [0, L+T) is cut into 128-key tiles; tiles lying wholly in the hidden
+// slot are excluded by arithmetic on the device-resident frame counter, the
+// remaining candidates are divided among the CTAs that share a query tile, and
+// each CTA scans `written` for its candidates and walks those that hold a
+// visible key.  Ring wrap-around therefore is only "which tiles are walked";
+// nothing is gathered or copied.
 //
-// One CTA = 128 queries of one (batch row, head) x one split of the tile
-// list.  Warp roles (384 threads):
-//   warps 0-3   softmax stream A: tiles 0, 2, 4, ... of the CTA's share
-//   warps 4-7   softmax stream B: tiles 1, 3, 5, ...
-//               Thread r of either group owns query row r (TMEM lane r), so
-//               row max and row sum are in-thread reductions.  Each stream
-//               keeps its own running maximum, row sum and O accumulator, so
-//               the two never synchronise; they are merged once at the end.
-//               exp2 with the scale folded in; the running maximum is raised
-//               (and O rescaled in tensor memory) only when it grew by more
-//               than 2^8; P (bf16/f16) overwrites the first half of its S.
-//   warp 8      producer: builds the visible-tile list on its own (no
-//               block-wide step), TMA-loads Q once and then the K tiles
-//               through a ring of shared-memory stages.
+// One CTA = 128 queries of one (batch row, head) x one split of the key tiles.
+// Warp roles (384 threads):
+//   warps 0-3   softmax group 0, warps 4-7 softmax group 1.  Thread r of either
+//               group owns query row r (TMEM lane r), so row max and row sum
+//               are in-thread reductions.  Group g handles keys [64g, 64g+64)
+//               of every tile as a stream of its own: running maximum, row
+//               sum and accumulator O_g; the two streams are merged once at
+//               the end.  exp2 with the scale folded in; the running maximum
+//               is raised (and O_g rescaled in tensor memory) only when it
+//               grew by more than 2^8; P (bf16/f16) overwrites the S columns
+//               the thread has consumed.
+//   warp 8      producer: barrier set-up, Q load, the first two K/V tiles
+//               (fetched before their visibility is known), then the K ring.
 //   warp 10     V producer: the V tiles through a ring of their own.
-//   warp 9      MMA issuer and TMEM owner: tcgen05.mma S = Q K^T (both
-//               operands in shared memory, K-major, 128-byte swizzle) and
-//               O += P V (P from tensor memory, V from shared memory as an
-//               MN-major operand), in the order S0 S1 PV0 S2 PV1 S3 ... so
-//               the tensor pipe works on one stream while the softmax warps
-//               work on the other.
-//   warp 11     idle (rounds the block up to three warpgroups).
-// Tensor memory (512 columns): S_A, S_B, O_A, O_B, 128 columns each.
+//   warp 9      MMA issuer and TMEM owner: tcgen05.mma S(i+1) = Q K^T (both
+//               operands in shared memory, K-major, 128-byte swizzle) ahead
+//               into the other S buffer, then O_g += P_g V_g for both key
+//               halves of tile i (P from tensor memory, V from shared memory
+//               as an MN-major operand).
+//   warp 11     compacts the visible-tile list; with the fused append, copies
+//               this CTA's share of the new K/V rows into the cache.
+// Tensor memory (512 columns): S0, S1, O_0, O_1, 128 columns each.
 //
-// Split-KV: when (batch x heads x query tiles) cannot fill the SMs, the tile
-// list is split over several CTAs.  Each writes its un-normalised O, row
-// maxima and row sums to the workspace; the CTA that arrives last at a
-// per-(row, head, query tile) ticket counter merges them in a fixed order and
-// writes the output.  Nobody spins on another CTA.
+// Split-KV: when (batch x heads x query tiles) cannot fill the SMs, the key
+// tiles of a query tile are split over 2, 4 or 8 CTAs that form a thread-block
+// cluster.  They exchange their rows' (max, sum) pairs with asynchronous
+// stores that complete on the peers' mbarriers, weight their partial rows,
+// and push each peer the rows it owns with one bulk copy; the owner adds them
+// in split order.  No cluster-wide barrier is on that path: peers signal each
+// other through mbarriers, every wait is bounded.  Where clusters of that size
+// cannot be scheduled the partials go through the caller's workspace instead
+// and the CTA that arrives last at a ticket counter merges them.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -169,9 +174,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__device__ __forceinline__ void cluster_arrive_release() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void cluster_arrive_relaxed() {
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }
@@ -232,22 +234,6 @@ __device__ __forceinline__ void st_async_f32x2(uint32_t dst_cluster_addr, float 
                    dst_cluster_addr),
                "f"(a), "f"(b), "r"(bar_cluster_addr)
                : "memory");
-}
-__device__ __forceinline__ void st_dsmem_f32x2(uint32_t addr, float a, float b) {
-  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
-}
-__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(addr)
-               : "memory");
-  return v;
-}
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
 }
 
 // Programmatic dependent launch: wait until the preceding kernel of the stream has completed and its
@@ -404,9 +390,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
   constexpr int kBlind = 2;                       // tiles loaded before their visibility is known
   const int nblind = np < kBlind ? np : kBlind;
+  // The visibility scan is done by every warp but the producer (warp 8), which fetches tiles meanwhile.
+  constexpr int kScanThreads = kAttnThreads - 32;
+  const int stid = tid < 256 ? tid : tid - 32;
   // this thread's first 16 tokens of `written` (of its candidate range), in flight during the set-up
-  const int my_j = tid >> 3;
-  const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (tid & 7) : 0x3FFFFFF, p.C);
+  const int my_j = stid >> 3;
+  const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (stid & 7) : 0x3FFFFFF, p.C);
   if (warp == 8) {
     // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final
     // [11] ml_bar [12] ack_bar, then the rings
@@ -437,15 +426,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int ch = 0; ch < Cfg::kChunks; ++ch)
         tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, v3[p.q_perm[0]], v3[p.q_perm[1]],
                     v3[p.q_perm[2]]);
-      // The first tiles of the range are fetched right away, before it is known whether they hold a visible
-      // key (they almost always do): DRAM latency then overlaps the rest of the prologue.  A tile that the
-      // preceding kernel (the append) may still be writing -- anything reaching into the tail -- waits for it.
-      for (int j = 0; j < nblind; ++j) {
-        const int key0 = phys_tile(c0 + j) * kBlockN;
-        if (key0 + kBlockN > p.L) grid_dependency_wait();
-        load_kv_tile(true, sK + j * Cfg::kTileBytes, &k_full[j], key0);
-        load_kv_tile(false, sV + j * Cfg::kTileBytes, &v_full[j], key0);
-      }
     }
   }
   if (warp == 9) {
@@ -463,20 +443,35 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem_base = *s_tmem;
 
   // ------------------------------------------------------ visible-tile list
-  // 16 tokens per thread, eight lanes make one 128-key tile; the per-tile counts of the CTA's candidates go
-  // to shared memory and the producer warp compacts them into the list of tiles to walk.
-  {
-    if (tid == 0) {
+  // The producer warp fetches the first tiles of the range right away, before it is known whether they hold a
+  // visible key (they almost always do; a miss is drained later): DRAM latency then overlaps the scan.  A
+  // tile that the preceding kernel (the append) may still be writing -- anything reaching into the tail --
+  // waits for that kernel.  All other warps scan `written`: 16 tokens per thread, eight lanes make one
+  // 128-key tile; warp 11 compacts the per-tile counts into the list of tiles to walk.
+  int n = 0;                 // tiles of this CTA with at least one visible key
+  uint32_t blind_vis = 0;    // bit j: the j-th tile loaded ahead of time turned out visible
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int j = 0; j < nblind; ++j) {
+        const int key0 = phys_tile(c0 + j) * kBlockN;
+        if (key0 + kBlockN > p.L) grid_dependency_wait();
+        load_kv_tile(true, sK + j * Cfg::kTileBytes, &k_full[j], key0);
+        load_kv_tile(false, sV + j * Cfg::kTileBytes, &v_full[j], key0);
+      }
+    }
+    __syncwarp();
+  } else {
+    if (stid == 0) {
       s_slot[0] = slot_base;
       s_slot[1] = hide_i;
     }
     const int nvec_pad = (np * 8 + 31) & ~31;      // whole warps take part in the shuffles
 #pragma unroll 1
-    for (int idx = tid; idx < nvec_pad; idx += kAttnThreads) {
+    for (int idx = stid; idx < nvec_pad; idx += kScanThreads) {
       const int j = idx >> 3;
       const int v = j < np ? phys_tile(c0 + j) * 8 + (idx & 7) : 0x3FFFFFF;
       uint4 w = w_first;
-      if (idx != tid) w = load_written16(wr, v, p.C);
+      if (idx != stid) w = load_written16(wr, v, p.C);
       const int k0 = v * 16;
       // one bit per non-zero byte
       const uint32_t nz0 = __vcmpne4(w.x, 0u) & 0x01010101u, nz1 = __vcmpne4(w.y, 0u) & 0x01010101u;
@@ -496,27 +491,27 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
       if ((lane & 7) == 0 && j < np) s_cnt[j] = static_cast<uint8_t>(cnt);
     }
-  }
-  __syncthreads();
-  int n = 0;                 // tiles of this CTA with at least one visible key
-  uint32_t blind_vis = 0;    // bit j: the j-th tile loaded ahead of time turned out visible
-  if (warp == 8) {
+    named_bar_sync(3, kScanThreads);
+    if (warp == 11) {
 #pragma unroll 1
-    for (int base = 0; base < np; base += 32) {
-      const int j = base + lane;
-      const int c = j < np ? s_cnt[j] : 0;
-      const unsigned m = __ballot_sync(0xffffffffu, c != 0);
-      if (c != 0)
-        s_list[n + __popc(m & ((1u << lane) - 1u))] =
-            static_cast<uint16_t>((phys_tile(c0 + j) << 1) | (c != kBlockN ? 1 : 0));
-      if (base == 0) blind_vis = m & ((1u << nblind) - 1u);
-      n += __popc(m);
+      for (int base = 0; base < np; base += 32) {
+        const int j = base + lane;
+        const int c = j < np ? s_cnt[j] : 0;
+        const unsigned m = __ballot_sync(0xffffffffu, c != 0);
+        if (c != 0)
+          s_list[n + __popc(m & ((1u << lane) - 1u))] =
+              static_cast<uint16_t>((phys_tile(c0 + j) << 1) | (c != kBlockN ? 1 : 0));
+        if (base == 0) blind_vis = m & ((1u << nblind) - 1u);
+        n += __popc(m);
+      }
+      if (lane == 0) {
+        s_nlist[0] = static_cast<uint32_t>(n);
+        s_nlist[1] = blind_vis;
+      }
+      __threadfence_block();
     }
-    if (lane == 0) {
-      s_nlist[0] = static_cast<uint32_t>(n);
-      s_nlist[1] = blind_vis;
-    }
-    __threadfence_block();
+  }
+  if (warp == 11) {
     named_bar_arrive(2, kAttnThreads);   // the other warps sleep on this barrier instead of polling
   } else {
     named_bar_sync(2, kAttnThreads);
