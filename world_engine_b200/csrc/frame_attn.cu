@@ -168,6 +168,32 @@ __device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Packed fp32 pairs (Blackwell executes fma / add on two floats per instruction).
+__device__ __forceinline__ uint64_t pk64(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void upk64(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t splat2(float x) { return pk64(__float_as_uint(x), __float_as_uint(x)); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -696,11 +722,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
-        for (int e = 0; e < 32; e += 4) {
-          mx4[0] = fmaxf(mx4[0], __uint_as_float(s[c][e + 0]));
-          mx4[1] = fmaxf(mx4[1], __uint_as_float(s[c][e + 1]));
-          mx4[2] = fmaxf(mx4[2], __uint_as_float(s[c][e + 2]));
-          mx4[3] = fmaxf(mx4[3], __uint_as_float(s[c][e + 3]));
+        for (int e = 0; e < 32; e += 8) {      // three-input max: two elements per instruction, four chains
+          mx4[0] = max3(mx4[0], __uint_as_float(s[c][e + 0]), __uint_as_float(s[c][e + 1]));
+          mx4[1] = max3(mx4[1], __uint_as_float(s[c][e + 2]), __uint_as_float(s[c][e + 3]));
+          mx4[2] = max3(mx4[2], __uint_as_float(s[c][e + 4]), __uint_as_float(s[c][e + 5]));
+          mx4[3] = max3(mx4[3], __uint_as_float(s[c][e + 6]), __uint_as_float(s[c][e + 7]));
         }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // A half tile may be fully masked (its visible keys all lie in the other half): keep the maximum finite
@@ -714,22 +740,54 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         l_run *= alpha;
         m_run = m_new;
       }
-      const float neg_m = -m_run;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(S * scale - m) on packed pairs.  The special-function unit does 16 exponentials per clock and
+      // SM and is the scarcest resource here, so 13 of the 32 pairs take a software path on the FMA pipe
+      // instead: round-to-nearest split x = r + f by the magic-number add, a degree-3 polynomial for 2^f on
+      // [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 resolution of P), and r added into the exponent.
+      const uint64_t scale2 = splat2(p.scale_log2), negm2 = splat2(-m_run);
+      const uint64_t magic2 = splat2(12582912.f), negmagic2 = splat2(-12582912.f), minus1_2 = splat2(-1.f);
+      const uint64_t c0_2 = splat2(0.9999281168f), c1_2 = splat2(0.6932609677f);
+      const uint64_t c2_2 = splat2(0.2426105440f), c3_2 = splat2(0.0551713258f);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t pk[32];
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 1);
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 2);
 #pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][2 * e]), p.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][2 * e + 1]), p.scale_log2, neg_m));
-          sum4[(2 * e) & 3] += p0;
-          sum4[(2 * e + 1) & 3] += p1;
-          pk[c * 16 + e] = pack2<BF16>(p0, p1);
+      for (int q = 0; q < 32; ++q) {
+        const int c = q >> 4, e = q & 15;
+        const uint64_t x2 = fma2(pk64(s[c][2 * e], s[c][2 * e + 1]), scale2, negm2);
+        uint32_t xl, xh, pl, ph;
+        upk64(x2, xl, xh);
+        if ((q % 5) == 1 || (q % 5) == 3) {
+          const uint64_t xc2 = pk64(__float_as_uint(fmaxf(__uint_as_float(xl), -125.f)),
+                                    __float_as_uint(fmaxf(__uint_as_float(xh), -125.f)));
+          const uint64_t t2 = add2(xc2, magic2);            // low mantissa bits = round(x)
+          const uint64_t r2 = add2(t2, negmagic2);          // round(x) as a float
+          const uint64_t f2 = fma2(r2, minus1_2, xc2);      // x - round(x) in [-0.5, 0.5]
+          uint64_t p2 = fma2(f2, c3_2, c2_2);
+          p2 = fma2(p2, f2, c1_2);
+          p2 = fma2(p2, f2, c0_2);
+          uint32_t tl, th, ql, qh;
+          upk64(t2, tl, th);
+          upk64(p2, ql, qh);
+          pl = ql + (tl << 23);                             // 2^f * 2^round(x)
+          ph = qh + (th << 23);
+        } else {
+          pl = __float_as_uint(fast_exp2(__uint_as_float(xl)));
+          ph = __float_as_uint(fast_exp2(__uint_as_float(xh)));
         }
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 3);
+        sum2[q & 3] = add2(sum2[q & 3], pk64(pl, ph));
+        pk[q] = pack2<BF16>(__uint_as_float(pl), __uint_as_float(ph));
+      }
+      float sum4[4];
+      {
+        const uint64_t t01 = add2(sum2[0], sum2[1]), t23 = add2(sum2[2], sum2[3]);
+        uint32_t a0, a1, b0, b1;
+        upk64(t01, a0, a1);
+        upk64(t23, b0, b1);
+        sum4[0] = __uint_as_float(a0);
+        sum4[1] = __uint_as_float(a1);
+        sum4[2] = __uint_as_float(b0);
+        sum4[3] = __uint_as_float(b1);
+      }
       tmem_st32(s_addr, pk);                                    // P over the S columns this thread has consumed
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
