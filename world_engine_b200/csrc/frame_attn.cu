@@ -35,13 +35,20 @@
 //               this CTA's share of the new K/V rows into the cache.
 // Tensor memory (512 columns): S0, S1, O_0, O_1, 128 columns each.
 //
+// The launch carries the programmatic-stream-serialization attribute: barrier
+// set-up, tensor-memory allocation and tensor-map prefetch run while the
+// preceding kernel of the stream drains; griddepcontrol.wait precedes the first
+// access to global memory, and dependents are released after the last tile.
+//
 // Split-KV: when (batch x heads x query tiles) cannot fill the SMs, the key
 // tiles of a query tile are split over 2, 4 or 8 CTAs that form a thread-block
-// cluster.  They exchange their rows' (max, sum) pairs with asynchronous
-// stores that complete on the peers' mbarriers, weight their partial rows,
-// and push each peer the rows it owns with one bulk copy; the owner adds them
-// in split order.  No cluster-wide barrier is on that path: peers signal each
-// other through mbarriers, every wait is bounded.  Where clusters of that size
+// cluster.  After its last tile a CTA sends its rows' (max, sum) pairs to the
+// peers with asynchronous stores that complete on the peers' mbarriers,
+// stages its partial rows (relative to its own maximum) in shared memory and
+// pushes each peer the rows that peer owns with one bulk copy; the owner
+// weights the rows of all splits by exp2(m_split - m_row) / l_row and adds
+// them in split order.  No cluster-wide barrier is on that path: peers signal
+// each other through mbarriers, every wait is bounded.  Where clusters of that size
 // cannot be scheduled the partials go through the caller's workspace instead
 // and the CTA that arrives last at a ticket counter merges them.
 #include <cuda.h>
@@ -222,37 +229,12 @@ __device__ __forceinline__ void bulk_copy_to_peer(uint32_t dst_cluster_addr, uin
       "r"(src_cta_addr), "r"(bytes), "r"(bar_cluster_addr)
       : "memory");
 }
-// Arrive (count 1) on an mbarrier in a peer CTA's shared memory.  Relaxed: a release fence at cluster scope
-// costs about half a microsecond, so callers that publish data issue ONE fence_cluster() before their arrivals.
+// Arrive (count 1) on an mbarrier in a peer CTA's shared memory.  Relaxed: it publishes no data, it only tells
+// the peer that something it sent has been consumed.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
-__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
-// Bounded wait with acquire at cluster scope, for barriers that peer CTAs arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
-  const uint64_t t0 = global_timer_ns();
-  uint32_t it = 0;
-  while (true) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    if ((++it & 63u) == 0u) {
-      if (*abort_word != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_word = 1;
-        return false;
-      }
-    }
-  }
-}
+
 // Asynchronous store of two floats into a peer CTA's shared memory; the 8 bytes are signalled on the peer's
 // mbarrier as transaction bytes, so the data is visible to whoever sees that barrier phase complete.
 __device__ __forceinline__ void st_async_f32x2(uint32_t dst_cluster_addr, float a, float b, uint32_t bar_cluster_addr) {
@@ -386,42 +368,23 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   // One K or V tile into a ring stage.  With the fused append the tiles of the tail frame come straight from
   // k_new / v_new (the copy into the cache happens on the side and is never read back in this launch).
+  // (coordinates are routed to the tensor map's axes with selects: an indexed array would live in local memory)
+  auto pick3 = [](int which, int a0, int a1, int a2) { return which == 0 ? a0 : (which == 1 ? a1 : a2); };
   auto load_kv_tile = [&](bool is_k, uint8_t* dst, uint64_t* bar, int key0) {
     const bool from_new = p.fused && key0 >= p.L;
     const CUtensorMap* tm = is_k ? (from_new ? &tm_kn : &tm_k) : (from_new ? &tm_vn : &tm_v);
     const int32_t* perm = from_new ? (is_k ? p.kn_perm : p.vn_perm) : p.kv_perm;
-    const int c3[3] = {from_new ? key0 - static_cast<int>(p.L) : key0, kvh, b};
+    const int tok = from_new ? key0 - static_cast<int>(p.L) : key0;
+    const int x1 = pick3(perm[0], tok, kvh, b), x2 = pick3(perm[1], tok, kvh, b), x3 = pick3(perm[2], tok, kvh, b);
     mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
-    for (int ch = 0; ch < Cfg::kChunks; ++ch)
-      tma_load_4d(dst + ch * Cfg::kChunkBytes, tm, bar, ch * 64, c3[perm[0]], c3[perm[1]], c3[perm[2]]);
+#pragma unroll
+    for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(dst + ch * Cfg::kChunkBytes, tm, bar, ch * 64, x1, x2, x3);
   };
 
   // ---------------------------------------------------------------- set-up
-  // Issue the only global loads of the prologue right away; they are consumed after the set-up barrier.
-  const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
+  // On-chip part first: it needs nothing from global memory, so it may run while the preceding kernel of the
+  // stream is still finishing (programmatic dependent launch).
   if (tid == 0) *s_abort = 0;
-  // Candidate tiles = physical tiles minus those that lie entirely in the hidden slot (pure arithmetic on
-  // the frame counter).  Split `split` owns candidates [c0, c1); which of them hold a visible key is decided
-  // below from `written`.
-  int slot_base, hide_i;
-  slot_of_fast(ft, p.L, p.T, p.dilation, p.ring_frames, slot_base, hide_i);
-  const int hid_lo = hide_i ? slot_base : 0, hid_hi = hide_i ? slot_base + p.T : 0;   // hidden token range
-  const int first_h = hide_i ? (slot_base + kBlockN - 1) / kBlockN : 0;
-  const int last_h = hide_i ? (slot_base + p.T) / kBlockN : 0;
-  const int count_h = last_h > first_h ? last_h - first_h : 0;
-  const int n_cand = p.ntiles - count_h;
-  const int c0 = static_cast<int>((static_cast<int64_t>(n_cand) * split) / p.nsplit);
-  const int c1 = static_cast<int>((static_cast<int64_t>(n_cand) * (split + 1)) / p.nsplit);
-  const int np = c1 - c0;
-  auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
-  constexpr int kBlind = 2;                       // tiles loaded before their visibility is known
-  const int nblind = np < kBlind ? np : kBlind;
-  // The visibility scan is done by every warp but the producer (warp 8), which fetches tiles meanwhile.
-  constexpr int kScanThreads = kAttnThreads - 32;
-  const int stid = tid < 256 ? tid : tid - 32;
-  // this thread's first 16 tokens of `written` (of its candidate range), in flight during the set-up
-  const int my_j = stid >> 3;
-  const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (stid & 7) : 0x3FFFFFF, p.C);
   if (warp == 8) {
     // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final
     // [11] ml_bar [12] ack_bar, then the rings
@@ -446,21 +409,72 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_arrive_expect_tx(ml_bar, static_cast<uint32_t>((p.nsplit - 1) * kBlockM * 8));
         mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRow * 4));
       }
-      // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
-      mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
-      const int v3[3] = {q0, h, b};
-      for (int ch = 0; ch < Cfg::kChunks; ++ch)
-        tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, v3[p.q_perm[0]], v3[p.q_perm[1]],
-                    v3[p.q_perm[2]]);
     }
+    __syncwarp();
+    named_bar_arrive(4, kAttnThreads);
   }
   if (warp == 9) {
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
+    if (lane == 0) WE_TRACE(8);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
+  // Everything below reads global memory that the preceding kernel of the stream may have produced (the
+  // queries, the new rows, the cache, the frame counter): wait until that kernel has completed and its writes
+  // are visible.  Returns at once when the launch carried no programmatic dependency.
+  if (tid == 0) WE_TRACE(4);
+  grid_dependency_wait();
+  if (tid == 0) WE_TRACE(5);
+  const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
+  // Candidate tiles = physical tiles minus those that lie entirely in the hidden slot (pure arithmetic on
+  // the frame counter).  Split `split` owns candidates [c0, c1); which of them hold a visible key is decided
+  // below from `written`.
+  int slot_base, hide_i;
+  slot_of_fast(ft, p.L, p.T, p.dilation, p.ring_frames, slot_base, hide_i);
+  if (tid == 0) WE_TRACE(6 + (slot_base & 0));
+  const int hid_lo = hide_i ? slot_base : 0, hid_hi = hide_i ? slot_base + p.T : 0;   // hidden token range
+  const int first_h = hide_i ? (slot_base + kBlockN - 1) / kBlockN : 0;
+  const int last_h = hide_i ? (slot_base + p.T) / kBlockN : 0;
+  const int count_h = last_h > first_h ? last_h - first_h : 0;
+  const int n_cand = p.ntiles - count_h;
+  const int c0 = static_cast<int>((static_cast<int64_t>(n_cand) * split) / p.nsplit);
+  const int c1 = static_cast<int>((static_cast<int64_t>(n_cand) * (split + 1)) / p.nsplit);
+  const int np = c1 - c0;
+  auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
+  constexpr int kBlind = 2;                       // tiles loaded before their visibility is known
+  const int nblind = np < kBlind ? np : kBlind;
+  // The visibility scan is done by every warp but the producer (warp 8), which fetches tiles meanwhile.
+  constexpr int kScanThreads = kAttnThreads - 32;
+  const int stid = tid < 256 ? tid : tid - 32;
+  // this thread's first 16 tokens of `written` (of its candidate range), in flight during the set-up
+  const int my_j = stid >> 3;
+  const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (stid & 7) : 0x3FFFFFF, p.C);
+  if (warp == 8 && lane == 0) {
+    // The first tiles of the range, before it is known whether they hold a visible key (they almost always
+    // do; a miss is drained later): DRAM latency then overlaps the rest of the set-up and the scan.  K(0) and
+    // Q, which the first product needs, go first.
+    if (nblind > 0) load_kv_tile(true, sK, &k_full[0], phys_tile(c0) * kBlockN);
+    {
+      // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
+      mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
+      const int x1 = pick3(p.q_perm[0], q0, h, b), x2 = pick3(p.q_perm[1], q0, h, b), x3 = pick3(p.q_perm[2], q0, h, b);
+#pragma unroll
+      for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, x1, x2, x3);
+    }
+    if (nblind > 0) load_kv_tile(false, sV, &v_full[0], phys_tile(c0) * kBlockN);
+    for (int j = 1; j < nblind; ++j) {
+      const int key0 = phys_tile(c0 + j) * kBlockN;
+      load_kv_tile(true, sK + j * Cfg::kTileBytes, &k_full[j], key0);
+      load_kv_tile(false, sV + j * Cfg::kTileBytes, &v_full[j], key0);
+    }
+    WE_TRACE(7);
+  }
+  // Set-up barrier.  The producer warp only arrives (it did so above, right after initialising the mbarriers):
+  // it needs nothing from the other warps and goes on issuing loads.
+  if (warp != 8) {
+    tc_fence_before();
+    named_bar_sync(4, kAttnThreads);
+    tc_fence_after();
+  }
   // Split-phase cluster barrier: "my barriers are initialised" now, awaited much later, right before the
   // first access to a peer's shared memory.
   // (relaxed: the barrier initialisation was already published by fence.mbarrier_init.release.cluster)
@@ -469,24 +483,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem_base = *s_tmem;
 
   // ------------------------------------------------------ visible-tile list
-  // The producer warp fetches the first tiles of the range right away, before it is known whether they hold a
-  // visible key (they almost always do; a miss is drained later): DRAM latency then overlaps the scan.  A
-  // tile that the preceding kernel (the append) may still be writing -- anything reaching into the tail --
-  // waits for that kernel.  All other warps scan `written`: 16 tokens per thread, eight lanes make one
-  // 128-key tile; warp 11 compacts the per-tile counts into the list of tiles to walk.
+  // While the first tiles are on their way, all warps but the producer scan `written`: 16 tokens per thread,
+  // eight lanes make one 128-key tile; warp 11 compacts the per-tile counts into the list of tiles to walk.
   int n = 0;                 // tiles of this CTA with at least one visible key
   uint32_t blind_vis = 0;    // bit j: the j-th tile loaded ahead of time turned out visible
-  if (warp == 8) {
-    if (lane == 0) {
-      for (int j = 0; j < nblind; ++j) {
-        const int key0 = phys_tile(c0 + j) * kBlockN;
-        if (key0 + kBlockN > p.L) grid_dependency_wait();
-        load_kv_tile(true, sK + j * Cfg::kTileBytes, &k_full[j], key0);
-        load_kv_tile(false, sV + j * Cfg::kTileBytes, &v_full[j], key0);
-      }
-    }
-    __syncwarp();
-  } else {
+  if (warp != 8) {
     if (stid == 0) {
       s_slot[0] = slot_base;
       s_slot[1] = hide_i;
@@ -555,12 +556,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
   // ------------------------------------------------------------------ roles
-  if (warp == 8 || warp == 10) {
-    // Everything above only needed data that existed before the preceding kernel of the stream (the
-    // append of this frame, when launched through we_b200_append_attend) began.  The cache contents it
-    // writes are needed from here on.
-    grid_dependency_wait();
-  }
   if (warp == 8) {
     if (lane == 0) {
       // K ring: a tile is issued as soon as the S that used its stage has completed.
@@ -638,7 +633,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_commit(&k_empty[sk]);
         tc_commit(&s_ready[i & 1]);
       };
+      WE_TRACE(9);
       issue_s(0);
+      WE_TRACE(10);
       for (int i = 0; i < n; ++i) {
         const int av = load_seq(i);
         const int sv = av % kStagesV;
@@ -843,14 +840,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint8_t* orow = static_cast<uint8_t*>(p.out) +
                     2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + col0);
     if (p.cluster_merge) {
-      // Weight of this split's row in the final result: exp2(m - m_row) / l_row over all splits.
-      float wgt;
+      float wgt = 1.0f;
       if (p.nsplit == 1) {
         wgt = 1.0f / l_cta;
       } else {
         cluster_wait_acquire();       // every CTA of the cluster has initialised its barriers (long ago)
         // every CTA of the cluster learns every split's (m, l): group 0 sends its rows' pair to all peers as
-        // asynchronous stores that complete on the peer's barrier (no fence, no extra arrival)
+        // asynchronous stores that complete on the peer's barrier (no fence, no extra arrival).  The pairs
+        // are consumed only when the rows are summed, so their flight overlaps the staging below.
         if (wg == 0) {
           const uint32_t mine = smem_u32(s_mltab + (split * kBlockM + row) * 2);
           const uint32_t bar = smem_u32(ml_bar);
@@ -858,24 +855,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (d != split)
               st_async_f32x2(dsmem_addr(mine, static_cast<uint32_t>(d)), m_cta, l_cta,
                              dsmem_addr(bar, static_cast<uint32_t>(d)));
+          s_mltab[(split * kBlockM + row) * 2 + 0] = m_cta;     // own pair
+          s_mltab[(split * kBlockM + row) * 2 + 1] = l_cta;
         }
-        s_mltab[(split * kBlockM + row) * 2 + 0] = m_cta;     // own pair (both groups write the same values)
-        s_mltab[(split * kBlockM + row) * 2 + 1] = l_cta;
-        // once all peers' pairs are here their main loops are over, so their V rings may be written
-        mbar_wait_cluster(ml_bar, 0, s_abort);
-        float m_all = -INFINITY;
-#pragma unroll 1
-        for (int s2 = 0; s2 < p.nsplit; ++s2) {
-          const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (s2 * kBlockM + row) * 2);
-          if (ml.y > 0.f) m_all = fmaxf(m_all, ml.x);
-        }
-        float den = 0.f;
-#pragma unroll 1
-        for (int s2 = 0; s2 < p.nsplit; ++s2) {
-          const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (s2 * kBlockM + row) * 2);
-          if (ml.y > 0.f) den += ml.y * fast_exp2(ml.x - m_all);
-        }
-        wgt = l_cta > 0.f ? fast_exp2(m_cta - m_all) / den : 0.f;
       }
       if (row == 0) WE_TRACE(232 + wg);
       if (p.nsplit == 1) {
@@ -904,7 +886,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       } else {
-        // this split's contribution to the final rows, already weighted: fp32 rows in the (idle) K ring
+        // this split's rows, relative to its own maximum m_cta and not yet normalised: fp32, in the (idle) K ring
         float* part = reinterpret_cast<float*>(sK);
         const float wa = w_g0 * wgt, wb = w_g1 * wgt;
 #pragma unroll 1
@@ -1057,61 +1039,107 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     float* part = reinterpret_cast<float*>(sK);
     float* recv = reinterpret_cast<float*>(sV);
     const int slot_floats = R * Cfg::kPartRow;
-    __syncthreads();                  // this CTA's weighted rows are complete
-    if (tid == 0) {
-      WE_TRACE(236);
-      for (int d = 0; d < ns; ++d) {
-        if (d == split) continue;
-        const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
-        const int my_slot = split < d ? split : split - 1;          // my position among d's peers
-        const uint32_t dst = dsmem_addr(smem_u32(sV) + static_cast<uint32_t>(my_slot * (d1 - d0) * Cfg::kPartRow * 4),
-                                        static_cast<uint32_t>(d));
-        const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
-        bulk_copy_to_peer(dst, smem_u32(part + d0 * Cfg::kPartRow), static_cast<uint32_t>((d1 - d0) * Cfg::kPartRow * 4),
-                          bar);
+    __syncthreads();                  // this CTA's rows are staged
+    // One courier thread per peer (the last of the threads that share row `peer`, which has the fewest columns
+    // to sum later) sends that peer its rows and, once this CTA's own inbox is full, the acknowledgement.
+    const int tpr = kAttnThreads / R;            // threads per row in the sum below
+    const int rl = tid / tpr;
+    const int cg0 = tid - rl * tpr;
+    const bool courier = cg0 == tpr - 1 && rl < ns && rl != split;
+    if (tid == 0) WE_TRACE(236);
+    if (courier) {
+      const int d = rl;
+      // once all peers' pairs are here their main loops are over, so their V rings may be written
+      mbar_wait(ml_bar, 0, s_abort);
+      const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
+      const int my_slot = split < d ? split : split - 1;          // my position among d's peers
+      const uint32_t dst = dsmem_addr(smem_u32(sV) + static_cast<uint32_t>(my_slot * (d1 - d0) * Cfg::kPartRow * 4),
+                                      static_cast<uint32_t>(d));
+      const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
+      bulk_copy_to_peer(dst, smem_u32(part + d0 * Cfg::kPartRow), static_cast<uint32_t>((d1 - d0) * Cfg::kPartRow * 4),
+                        bar);
+    }
+    // (asynchronous stores and bulk copies complete on the barrier through the async proxy, like any TMA
+    // copy: the ordinary wait of the receiving CTA orders the data)
+    mbar_wait(ml_bar, 0, s_abort);           // all pairs present
+    if (tid == 0) WE_TRACE(242);
+    // 3 * ns threads share one of the R = 128 / ns rows; each takes every (3 ns)-th group of 4 columns.  Split
+    // u's row enters with the weight exp2(m_u - m_row) / l_row, l_row = sum over splits of l_u exp2(m_u - m_row),
+    // computed once per thread.
+    {
+      constexpr int kGroups = DH / 4;
+      const int row = r0 + rl;
+      float w_u[8], l_u[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        w_u[u] = -INFINITY;
+        l_u[u] = 0.f;
+        if (u < ns) {
+          const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (u * kBlockM + row) * 2);
+          l_u[u] = ml.y;
+          w_u[u] = ml.y > 0.f ? ml.x : -INFINITY;
+        }
       }
-    }
-    mbar_wait(recv_bar, 0, s_abort);   // the rows of all peers have landed
-    if (tid == 0) {
-      WE_TRACE(237);
-      // acknowledge to every sender: its staging buffer is no longer read
-      for (int d = 0; d < ns; ++d)
-        if (d != split) mbar_arrive_remote(dsmem_addr(smem_u32(ack_bar), static_cast<uint32_t>(d)));
-    }
-    // One item = one row x 4 consecutive columns; consecutive lanes take consecutive columns of a row.
-    constexpr int kGroups = DH / 4;
-    const int items = R * kGroups;
-#pragma unroll 1
-    for (int it = tid; it < items; it += kAttnThreads) {
-      const int rl = it / kGroups;
-      const int c0 = (it - rl * kGroups) * 4;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float m_all = fmaxf(fmaxf(fmaxf(w_u[0], w_u[1]), fmaxf(w_u[2], w_u[3])),
+                                fmaxf(fmaxf(w_u[4], w_u[5]), fmaxf(w_u[6], w_u[7])));
+#pragma unroll
+      for (int u = 0; u < 8; ++u) w_u[u] = l_u[u] > 0.f ? fast_exp2(w_u[u] - m_all) : 0.f;
+      const float den = (fmaf(l_u[0], w_u[0], l_u[1] * w_u[1]) + fmaf(l_u[2], w_u[2], l_u[3] * w_u[3])) +
+                        (fmaf(l_u[4], w_u[4], l_u[5] * w_u[5]) + fmaf(l_u[6], w_u[6], l_u[7] * w_u[7]));
+      const float inv = den > 0.f ? __fdividef(1.0f, den) : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) w_u[u] *= inv;
+      if (tid == 0) WE_TRACE(239);
+      mbar_wait(recv_bar, 0, s_abort);         // the rows of all peers have landed
+      if (tid == 0) WE_TRACE(237);
+      // acknowledge to the sender: its staging buffer is no longer read
+      if (courier) mbar_arrive_remote(dsmem_addr(smem_u32(ack_bar), static_cast<uint32_t>(rl)));
+      uint8_t* orow = static_cast<uint8_t*>(p.out) +
+                      2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2]);
+      const bool in_range = q0 + row < p.T;
+      // all loads first (at most 6 column groups per thread), then the stores: nothing orders them behind
+      // one another
+      constexpr int kMaxIt = 6;
+      float4 acc[kMaxIt];
+#pragma unroll
+      for (int k = 0; k < kMaxIt; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         if (u < ns) {
-          const float* src = u == split ? part + (r0 + rl) * Cfg::kPartRow
+          const float* src = u == split ? part + row * Cfg::kPartRow
                                         : recv + (u < split ? u : u - 1) * slot_floats + rl * Cfg::kPartRow;
-          const float4 v = *reinterpret_cast<const float4*>(src + c0);
-          acc.x += v.x;
-          acc.y += v.y;
-          acc.z += v.z;
-          acc.w += v.w;
+          const float w = w_u[u];
+#pragma unroll
+          for (int k = 0; k < kMaxIt; ++k) {
+            const int cg = cg0 + k * tpr;
+            if (cg < kGroups) {
+              const float4 v = *reinterpret_cast<const float4*>(src + cg * 4);
+              acc[k].x = fmaf(w, v.x, acc[k].x);
+              acc[k].y = fmaf(w, v.y, acc[k].y);
+              acc[k].z = fmaf(w, v.z, acc[k].z);
+              acc[k].w = fmaf(w, v.w, acc[k].w);
+            }
+          }
         }
       }
-      const int row = r0 + rl;
-      if (q0 + row < p.T) {
-        uint8_t* o = static_cast<uint8_t*>(p.out) +
-                     2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2] + c0);
-        uint2 v2;
-        v2.x = pack2<BF16>(acc.x, acc.y);
-        v2.y = pack2<BF16>(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(o) = v2;
+      if (in_range) {
+#pragma unroll
+        for (int k = 0; k < kMaxIt; ++k) {
+          const int cg = cg0 + k * tpr;
+          if (cg < kGroups) {
+            uint2 v2;
+            v2.x = pack2<BF16>(acc[k].x, acc[k].y);
+            v2.y = pack2<BF16>(acc[k].z, acc[k].w);
+            *reinterpret_cast<uint2*>(orow + cg * 8) = v2;
+          }
+        }
       }
     }
     if (tid == 0) WE_TRACE(238);
+    if (tid == kAttnThreads - 1) WE_TRACE(241);
     // This CTA may leave once every peer has acknowledged the rows pushed to it; nothing else of this CTA is
     // touched by a peer after that (their pairs and rows arrived before this CTA summed).
-    mbar_wait_cluster(ack_bar, 0, s_abort);
+    mbar_wait(ack_bar, 0, s_abort);
   }
 
   // --------------------------------------------------------------- teardown
@@ -1305,9 +1333,11 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
     attr[n_attr].val.clusterDim.z = 1;
     ++n_attr;
   }
-  if (overlap_previous_kernel) {
-    // Programmatic dependent launch: the CTAs may start while the preceding kernel of the stream (the append)
-    // is still draining; the kernel waits for it (griddepcontrol.wait) before it touches the cache contents.
+  (void)overlap_previous_kernel;
+  {
+    // Programmatic dependent launch, always: the CTAs may be scheduled while the preceding kernel of the
+    // stream is still draining (if that kernel allows it; otherwise this is an ordinary launch).  The kernel
+    // waits for its predecessor (griddepcontrol.wait) before its first access to global memory.
     attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
     ++n_attr;
