@@ -45,9 +45,9 @@ extern "C" int we_b200_append_attend(const void* q, const int64_t* q_strides_hos
                                      size_t workspace_bytes, int32_t* status, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // One launch does both when the tail frame is made of whole 128-key tiles and nobody asked for the
-  // visibility vector: the attention kernel reads the new frame from k_new / v_new and copies it into the
-  // cache on the side.  Otherwise: the append kernel, then the attention kernel (which overlaps its prologue
-  // with the append through programmatic dependent launch).
+  // visibility vector: the attention kernel reads the tiles of the new frame from k_new / v_new and stores them
+  // from shared memory into the cache.  Otherwise: the append kernel, then the attention kernel (which overlaps
+  // its on-chip set-up with the append through programmatic dependent launch).
   const bool two_byte = geom_host != nullptr && (geom_host->dtype == WE_B200_BF16 || geom_host->dtype == WE_B200_F16);
   if (two_byte && mask_written == nullptr && geom_host->T % 128 == 0 && geom_host->L % 128 == 0 && k_new && v_new &&
       kv && written && geom_host->Dh % 8 == 0) {

@@ -26,13 +26,16 @@
 //   warp 8      producer: barrier set-up, Q load, the first two K/V tiles
 //               (fetched before their visibility is known), then the K ring.
 //   warp 10     V producer: the V tiles through a ring of their own.
+//               With the fused append both producers also persist the tiles
+//               of the new frame that pass through their rings: tensor stores
+//               from shared memory into the tail slice and the ring slot.
 //   warp 9      MMA issuer and TMEM owner: tcgen05.mma S(i+1) = Q K^T (both
 //               operands in shared memory, K-major, 128-byte swizzle) ahead
 //               into the other S buffer, then O_g += P_g V_g for both key
 //               halves of tile i (P from tensor memory, V from shared memory
 //               as an MN-major operand).
-//   warp 11     compacts the visible-tile list; with the fused append, copies
-//               this CTA's share of the new K/V rows into the cache.
+//   warp 11     compacts the visible-tile list; with the fused append, marks
+//               the ring slot as written.
 // Tensor memory (512 columns): S0, S1, O_0, O_1, 128 columns each.
 //
 // The launch carries the programmatic-stream-serialization attribute: barrier
@@ -114,18 +117,13 @@ struct AttnParams {
   int32_t* ws_cnt;               // [unit]
   int32_t* status;
   int32_t cluster_merge;         // 1: the splits of a query tile form a thread-block cluster and merge through DSMEM
-  // fused append (we_b200_append_attend on tile-aligned caches): the new frame is read from k_new / v_new
-  // instead of the tail, and the CTAs of a kv head share the copy of that head's new rows into the cache
+  // fused append (we_b200_append_attend on tile-aligned caches): the tiles of the new frame are read from
+  // k_new / v_new (tensor maps of their own) instead of the tail, and stored from shared memory into the cache
+  // through the cache's tensor maps
   int32_t fused;
   int32_t is_frozen;
   int32_t kn_perm[3], vn_perm[3];
-  const uint4* k_new;
-  const uint4* v_new;
-  int64_t kn_s[3], vn_s[3];      // strides (b, h, t) of k_new / v_new in 16-byte vectors
-  uint4* kv_w;                   // the cache, writable
   uint8_t* written_w;
-  int64_t plane_stride_v, batch_stride_v;   // cache strides in 16-byte vectors
-  int32_t vpr;                   // 16-byte vectors per (token, head) row
 };
 
 #ifdef WE_ATTN_DEBUG
@@ -381,6 +379,23 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(dst + ch * Cfg::kChunkBytes, tm, bar, ch * 64, x1, x2, x3);
   };
 
+  // With the fused append, the CTAs of the first query tile and first query head of a kv head also persist the
+  // tiles of the new frame that pass through their rings: one tensor store from shared memory into the tail
+  // slice and, on an unfrozen write step, one into the ring slot (LayerKVCache.upsert,
+  // src/model/kv_cache.py:138,147-150).  The stores un-swizzle on the way out, like the loads swizzled.
+  const bool storer = p.fused && qt == 0 && h == kvh * (p.Hq / p.Hkv);
+  auto store_kv_tile = [&](bool is_k, const uint8_t* src, int key0, bool to_ring, int slot_base) {
+    const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
+#pragma unroll 1
+    for (int dst = 0; dst < (to_ring ? 2 : 1); ++dst) {
+      const int tok = dst == 0 ? key0 : key0 - static_cast<int>(p.L) + slot_base;
+      const int x1 = pick3(p.kv_perm[0], tok, kvh, b), x2 = pick3(p.kv_perm[1], tok, kvh, b),
+                x3 = pick3(p.kv_perm[2], tok, kvh, b);
+#pragma unroll
+      for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_store_4d(tm, src + ch * Cfg::kChunkBytes, ch * 64, x1, x2, x3);
+    }
+  };
+
   // ---------------------------------------------------------------- set-up
   // On-chip part first: it needs nothing from global memory, so it may run while the preceding kernel of the
   // stream is still finishing (programmatic dependent launch).
@@ -395,9 +410,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(bars + lane, (lane >= 4 && lane < 8) ? kBlockM : (lane == 12 ? peers : 1));
     }
     if (lane == 0) {
-      prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
+      prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_v);
+      if (p.fused) {
+        prefetch_tensormap(&tm_kn);
+        prefetch_tensormap(&tm_vn);
+      }
     }
     __syncwarp();
     if (lane == 0) {
@@ -556,46 +575,56 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
   // ------------------------------------------------------------------ roles
-  if (warp == 8) {
+  if (warp == 8 || warp == 10) {
+    // Producers: warp 8 feeds the K ring, warp 10 the V ring (a ring of its own, so that a full V ring never
+    // holds back a K load).  A tile is issued as soon as the product that used its stage has completed.
     if (lane == 0) {
-      // K ring: a tile is issued as soon as the S that used its stage has completed.
-      for (int i = 0; i < n; ++i) {
-        const int a = load_seq(i);
-        if (a < nblind) continue;                    // fetched ahead of time
-        const int sk = a % kStagesK;
-        const int key0 = (s_list[i] >> 1) * kBlockN;
-        if (a >= kStagesK) mbar_wait(&k_empty[sk], ((a / kStagesK) - 1) & 1, s_abort);
-        if (i < 32) WE_TRACE(192 + i);
-#ifdef WE_ATTN_DEBUG
-        if (g_mode & 4) {   // experiment: no copy, the stage keeps what it held
-          mbar_arrive(&k_full[sk]);
-          continue;
+      const bool is_k = warp == 8;
+      uint8_t* ring = is_k ? sK : sV;
+      uint64_t* full = is_k ? k_full : v_full;
+      uint64_t* empty = is_k ? k_empty : v_empty;
+      const int stages = is_k ? kStagesK : kStagesV;
+      const int nloads = nblind + n - n_vis_blind;
+      const bool to_ring = !p.is_frozen && hide_i;
+      auto key_of = [&](int a) {
+        return (a < nblind ? phys_tile(c0 + a) : (s_list[a - nblind + n_vis_blind] >> 1)) * kBlockN;
+      };
+      for (int a = nblind; a < nloads; ++a) {
+        const int st = a % stages;
+        if (a >= stages) {
+          mbar_wait(&empty[st], ((a / stages) - 1) & 1, s_abort);
+          if (storer) {
+            // the tile that leaves the stage belongs to the new frame: persist it before the stage is refilled
+            const int kp = key_of(a - stages);
+            if (kp >= p.L) {
+              store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
+              bulk_commit_group();
+              bulk_wait_group_read0();
+            }
+          }
         }
-#endif
-        load_kv_tile(true, sK + sk * Cfg::kTileBytes, &k_full[sk], key0);
+        if (is_k && a - nblind < 32) WE_TRACE(192 + a - nblind);
+        load_kv_tile(is_k, ring + st * Cfg::kTileBytes, &full[st], key_of(a));
       }
-      if (n == 0) mbar_wait(q_full, 0, s_abort);  // nobody else consumes Q: let the copy land before exit
+      if (storer) {
+        // new-frame tiles still resident in the ring (the last loads): wait for them to land, persist them
+        for (int a = nloads > stages ? nloads - stages : 0; a < nloads; ++a) {
+          const int kp = key_of(a);
+          if (kp >= p.L) {
+            const int st = a % stages;
+            mbar_wait(&full[st], (a / stages) & 1, s_abort);
+            store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
+          }
+        }
+        bulk_commit_group();
+        bulk_wait_group_read0();
+      }
+      if (is_k && n == 0) mbar_wait(q_full, 0, s_abort);  // nobody else consumes Q: let the copy land before exit
     }
     __syncwarp();
-  } else if (warp == 10) {
-    if (lane == 0) {
-      // V ring, on its own thread so that a full V ring never holds back a K load.
-      for (int i = 0; i < n; ++i) {
-        const int a = load_seq(i);
-        if (a < nblind) continue;
-        const int sv = a % kStagesV;
-        const int key0 = (s_list[i] >> 1) * kBlockN;
-        if (a >= kStagesV) mbar_wait(&v_empty[sv], ((a / kStagesV) - 1) & 1, s_abort);
-#ifdef WE_ATTN_DEBUG
-        if (g_mode & 4) {
-          mbar_arrive(&v_full[sv]);
-          continue;
-        }
-#endif
-        load_kv_tile(false, sV + sv * Cfg::kTileBytes, &v_full[sv], key0);
-      }
-    }
-    __syncwarp();
+    // the rings are no longer read by stores of this warp: the epilogue may lay its exchange buffers over them
+    named_bar_arrive(5, kSoftmaxThreads + 64);
+    if (lane == 0 && storer) bulk_wait_group0();   // global writes performed before the CTA can exit
   } else if (warp == 9) {
     if (lane == 0) {
       // tiles fetched ahead of time that hold no visible key: let them land, then free their stages
@@ -822,6 +851,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(o_final, 0, s_abort);   // (the per-tile barriers of the other group were never followed here)
       tc_fence_after();
     }
+    // the producer warps are done with the rings (tensor stores of new-frame tiles have read them)
+    named_bar_sync(5, kSoftmaxThreads + 64);
     if (row == 0) WE_TRACE(224 + wg);
     // merge the two groups' streams: exchange (m, l); each group then combines one half of the head dim
     s_x[(wg * 2 + 0) * kBlockM + row] = m_run;
@@ -982,49 +1013,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
     }
   } else {
-    // warp 11: the append.  The CTAs that work on one kv head share the copy of that head's new K and V rows
-    // into the tail slice and, on an unfrozen write step, into the ring slot (LayerKVCache.upsert,
-    // src/model/kv_cache.py:138,147-151); one 16-byte vector per lane and step, 4 steps in flight.
-    if (p.fused) {
-      const int group = p.Hq / p.Hkv;
-      const int ctas = group * p.n_qtiles * p.nsplit;               // CTAs per (batch row, kv head)
-      const int rank = ((h - kvh * group) * p.n_qtiles + qt) * p.nsplit + split;
-      const int ra = (p.T * rank) / ctas, rb = (p.T * (rank + 1)) / ctas;
-      const bool to_ring = !p.is_frozen && hide_i;
-      const int64_t C64 = p.C;
-      const int nvec = (rb - ra) * p.vpr * 2;                       // K rows then V rows
-#pragma unroll 1
-      for (int base = 0; base < nvec; base += 128) {
-        uint4 val[4];
-        int64_t dst_tail[4];
-        int tok[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int idx = base + u * 32 + lane;
-          tok[u] = -1;
-          if (idx < nvec) {
-            const int plane = idx >= (nvec >> 1) ? 1 : 0;
-            const int rem = idx - plane * (nvec >> 1);
-            const int t = ra + rem / p.vpr;
-            const int v = rem - (rem / p.vpr) * p.vpr;
-            const uint4* src = plane ? p.v_new : p.k_new;
-            const int64_t* st = plane ? p.vn_s : p.kn_s;
-            val[u] = src[b * st[0] + kvh * st[1] + t * st[2] + v];
-            dst_tail[u] = plane * p.plane_stride_v + b * p.batch_stride_v + (kvh * C64 + p.L + t) * p.vpr + v;
-            tok[u] = (plane == 0 && v == 0 && kvh == 0) ? t : -2;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (tok[u] != -1) {
-            p.kv_w[dst_tail[u]] = val[u];                                         // tail, always
-            if (to_ring) {
-              p.kv_w[dst_tail[u] + (static_cast<int64_t>(slot_base) - p.L) * p.vpr] = val[u];   // ring slot
-              if (tok[u] >= 0) p.written_w[b * p.written_batch_stride + slot_base + tok[u]] = 1;
-            }
-          }
-        }
-      }
+    // warp 11: with the fused append on an unfrozen write step, one CTA per batch row marks the ring slot as
+    // written (LayerKVCache.upsert, src/model/kv_cache.py:151); the rows themselves are persisted by the
+    // producer warps of the CTAs whose rings they pass through.
+    if (p.fused && !p.is_frozen && hide_i && h == 0 && qt == 0 && split == 0) {
+      uint8_t* w = p.written_w + b * p.written_batch_stride + slot_base;
+      for (int t = lane; t < p.T; t += 32) w[t] = 1;
     }
   }
 
@@ -1416,9 +1410,13 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   tvn = tv;
   p.fused = 0;
   p.is_frozen = 0;
+  p.written_w = nullptr;
+  for (int i = 0; i < 3; ++i) p.kn_perm[i] = p.vn_perm[i] = i;
   if (fa != nullptr) {
-    // the append rides along: new rows are read through their own tensor maps and copied by one warp per CTA
+    // the append rides along: new rows are read through their own tensor maps and written back through the
+    // cache's maps, so the writable cache pointer must be the buffer the maps were made for
     if (!fa->k_new || !fa->v_new || !fa->kv_w || !fa->written_w) return WE_B200_E_NULL;
+    if (fa->kv_w != kv) return WE_B200_E_SHAPE;
     if ((rc = check_strides(fa->ks, 2)) != WE_B200_OK) return rc;
     if ((rc = check_strides(fa->vs, 2)) != WE_B200_OK) return rc;
     if (!aligned16(fa->k_new) || !aligned16(fa->v_new)) return WE_B200_E_ALIGN;
@@ -1426,17 +1424,7 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
     if ((rc = make_map(&tvn, fa->v_new, g->dtype, g->T, g->Hkv, g->B, g->Dh, fa->vs, p.vn_perm)) != WE_B200_OK) return rc;
     p.fused = 1;
     p.is_frozen = fa->is_frozen ? 1 : 0;
-    p.k_new = static_cast<const uint4*>(fa->k_new);
-    p.v_new = static_cast<const uint4*>(fa->v_new);
-    for (int i = 0; i < 3; ++i) {
-      p.kn_s[i] = fa->ks[i] / 8;
-      p.vn_s[i] = fa->vs[i] / 8;
-    }
-    p.kv_w = static_cast<uint4*>(fa->kv_w);
     p.written_w = fa->written_w;
-    p.plane_stride_v = g->kv_plane_stride / 8;
-    p.batch_stride_v = g->kv_batch_stride / 8;
-    p.vpr = g->Dh / 8;
   }
   dim3 grid(static_cast<unsigned>(sp.n_qtiles * sp.nsplit), static_cast<unsigned>(Hq), static_cast<unsigned>(g->B));
   if (g->Dh == 128) {
