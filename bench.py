@@ -43,7 +43,7 @@ N_LAYERS = 24
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu captures
 # summarised under profiles/ (bytes); None where no capture exists for that workload.
-NCU_TRAFFIC_BYTES = {"cfg2": 34.8e6, "cfg4": None, "cfg5": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 34.71e6, "cfg4": None, "cfg5": None}
 WORKLOAD = ("cfg2: B=1 H=16 Dh=128 T=256, 16-frame ring wrapped (frame_t=27, slot 11), bf16, append included; "
             "one step = 24 distinct layer caches (855 MB > L2, no flush needed)")
 
