@@ -60,6 +60,7 @@
 #include <math.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -929,16 +930,32 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_ld_wait();
           }
           float4* dst = reinterpret_cast<float4*>(part + row * Cfg::kPartRow + col0 + c * 32);
+          if (n > 0 && wa != 0.f && wb != 0.f) {
+            // both streams contribute (the usual case): packed pairs, two instructions per pair
+            const uint64_t wa2 = splat2(wa), wb2 = splat2(wb);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (n > 0) {
-              v.x = merge2(__uint_as_float(oa[4 * e + 0]), wa, __uint_as_float(ob[4 * e + 0]), wb);
-              v.y = merge2(__uint_as_float(oa[4 * e + 1]), wa, __uint_as_float(ob[4 * e + 1]), wb);
-              v.z = merge2(__uint_as_float(oa[4 * e + 2]), wa, __uint_as_float(ob[4 * e + 2]), wb);
-              v.w = merge2(__uint_as_float(oa[4 * e + 3]), wa, __uint_as_float(ob[4 * e + 3]), wb);
+            for (int e = 0; e < 8; ++e) {
+              const uint64_t lo = fma2(pk64(oa[4 * e + 0], oa[4 * e + 1]), wa2,
+                                       fma2(pk64(ob[4 * e + 0], ob[4 * e + 1]), wb2, 0ull));
+              const uint64_t hi = fma2(pk64(oa[4 * e + 2], oa[4 * e + 3]), wa2,
+                                       fma2(pk64(ob[4 * e + 2], ob[4 * e + 3]), wb2, 0ull));
+              uint32_t x, y, z, w;
+              upk64(lo, x, y);
+              upk64(hi, z, w);
+              dst[e] = make_float4(__uint_as_float(x), __uint_as_float(y), __uint_as_float(z), __uint_as_float(w));
             }
-            dst[e] = v;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (n > 0) {
+                v.x = merge2(__uint_as_float(oa[4 * e + 0]), wa, __uint_as_float(ob[4 * e + 0]), wb);
+                v.y = merge2(__uint_as_float(oa[4 * e + 1]), wa, __uint_as_float(ob[4 * e + 1]), wb);
+                v.z = merge2(__uint_as_float(oa[4 * e + 2]), wa, __uint_as_float(ob[4 * e + 2]), wb);
+                v.w = merge2(__uint_as_float(oa[4 * e + 3]), wa, __uint_as_float(ob[4 * e + 3]), wb);
+              }
+              dst[e] = v;
+            }
           }
         }
         fence_proxy_async_smem();        // the rows are read by bulk copies (async proxy) below
@@ -1033,6 +1050,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     float* part = reinterpret_cast<float*>(sK);
     float* recv = reinterpret_cast<float*>(sV);
     const int slot_floats = R * Cfg::kPartRow;
+    if (lane == 0) WE_TRACE(244 + warp);
     __syncthreads();                  // this CTA's rows are staged
     // One courier thread per peer (the last of the threads that share row `peer`, which has the fewest columns
     // to sum later) sends that peer its rows and, once this CTA's own inbox is full, the acknowledgement.
@@ -1059,30 +1077,31 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (tid == 0) WE_TRACE(242);
     // 3 * ns threads share one of the R = 128 / ns rows; each takes every (3 ns)-th group of 4 columns.  Split
     // u's row enters with the weight exp2(m_u - m_row) / l_row, l_row = sum over splits of l_u exp2(m_u - m_row),
-    // computed once per thread.
-    {
+    // computed once per thread.  Compiled once per split count, so that no loop carries dead iterations.
+    auto sum_rows = [&](auto ns_const) {
+      constexpr int NS = decltype(ns_const)::value;
       constexpr int kGroups = DH / 4;
+      constexpr int kTpr = 3 * NS;                                  // = kAttnThreads / (kBlockM / NS)
+      constexpr int kMaxIt = (kGroups + kTpr - 1) / kTpr;
       const int row = r0 + rl;
-      float w_u[8], l_u[8];
+      float w_u[NS], l_u[NS];
+      float m_all = -INFINITY;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        w_u[u] = -INFINITY;
-        l_u[u] = 0.f;
-        if (u < ns) {
-          const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (u * kBlockM + row) * 2);
-          l_u[u] = ml.y;
-          w_u[u] = ml.y > 0.f ? ml.x : -INFINITY;
-        }
+      for (int u = 0; u < NS; ++u) {
+        const float2 ml = *reinterpret_cast<const float2*>(s_mltab + (u * kBlockM + row) * 2);
+        l_u[u] = ml.y;
+        w_u[u] = ml.y > 0.f ? ml.x : -INFINITY;
+        m_all = fmaxf(m_all, w_u[u]);
       }
-      const float m_all = fmaxf(fmaxf(fmaxf(w_u[0], w_u[1]), fmaxf(w_u[2], w_u[3])),
-                                fmaxf(fmaxf(w_u[4], w_u[5]), fmaxf(w_u[6], w_u[7])));
+      float den = 0.f;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) w_u[u] = l_u[u] > 0.f ? fast_exp2(w_u[u] - m_all) : 0.f;
-      const float den = (fmaf(l_u[0], w_u[0], l_u[1] * w_u[1]) + fmaf(l_u[2], w_u[2], l_u[3] * w_u[3])) +
-                        (fmaf(l_u[4], w_u[4], l_u[5] * w_u[5]) + fmaf(l_u[6], w_u[6], l_u[7] * w_u[7]));
+      for (int u = 0; u < NS; ++u) {
+        w_u[u] = l_u[u] > 0.f ? fast_exp2(w_u[u] - m_all) : 0.f;
+        den = fmaf(l_u[u], w_u[u], den);
+      }
       const float inv = den > 0.f ? __fdividef(1.0f, den) : 0.f;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) w_u[u] *= inv;
+      for (int u = 0; u < NS; ++u) w_u[u] *= inv;
       if (tid == 0) WE_TRACE(239);
       mbar_wait(recv_bar, 0, s_abort);         // the rows of all peers have landed
       if (tid == 0) WE_TRACE(237);
@@ -1091,36 +1110,33 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2]);
       const bool in_range = q0 + row < p.T;
-      // all loads first (at most 6 column groups per thread), then the stores: nothing orders them behind
-      // one another
-      constexpr int kMaxIt = 6;
+      // all loads first, then the stores: nothing orders them behind one another
       float4 acc[kMaxIt];
 #pragma unroll
       for (int k = 0; k < kMaxIt; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (u < ns) {
-          const float* src = u == split ? part + row * Cfg::kPartRow
-                                        : recv + (u < split ? u : u - 1) * slot_floats + rl * Cfg::kPartRow;
-          const float w = w_u[u];
+      for (int u = 0; u < NS; ++u) {
+        const float* src = u == split ? part + row * Cfg::kPartRow
+                                      : recv + (u < split ? u : u - 1) * slot_floats + rl * Cfg::kPartRow;
+        const float w = w_u[u];
 #pragma unroll
-          for (int k = 0; k < kMaxIt; ++k) {
-            const int cg = cg0 + k * tpr;
-            if (cg < kGroups) {
-              const float4 v = *reinterpret_cast<const float4*>(src + cg * 4);
-              acc[k].x = fmaf(w, v.x, acc[k].x);
-              acc[k].y = fmaf(w, v.y, acc[k].y);
-              acc[k].z = fmaf(w, v.z, acc[k].z);
-              acc[k].w = fmaf(w, v.w, acc[k].w);
-            }
+        for (int k = 0; k < kMaxIt; ++k) {
+          const int cg = cg0 + k * kTpr;
+          if ((k + 1) * kTpr <= kGroups || cg < kGroups) {
+            const float4 v = *reinterpret_cast<const float4*>(src + cg * 4);
+            acc[k].x = fmaf(w, v.x, acc[k].x);
+            acc[k].y = fmaf(w, v.y, acc[k].y);
+            acc[k].z = fmaf(w, v.z, acc[k].z);
+            acc[k].w = fmaf(w, v.w, acc[k].w);
           }
         }
       }
+      if (tid == 0) WE_TRACE(243);
       if (in_range) {
 #pragma unroll
         for (int k = 0; k < kMaxIt; ++k) {
-          const int cg = cg0 + k * tpr;
-          if (cg < kGroups) {
+          const int cg = cg0 + k * kTpr;
+          if ((k + 1) * kTpr <= kGroups || cg < kGroups) {
             uint2 v2;
             v2.x = pack2<BF16>(acc[k].x, acc[k].y);
             v2.y = pack2<BF16>(acc[k].z, acc[k].w);
@@ -1128,7 +1144,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       }
-    }
+    };
+    if (ns == 2) sum_rows(std::integral_constant<int, 2>{});
+    else if (ns == 4) sum_rows(std::integral_constant<int, 4>{});
+    else sum_rows(std::integral_constant<int, 8>{});
     if (tid == 0) WE_TRACE(238);
     if (tid == kAttnThreads - 1) WE_TRACE(241);
     // This CTA may leave once every peer has acknowledged the rows pushed to it; nothing else of this CTA is
