@@ -1,6 +1,6 @@
 """Builds libwe_b200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-Usage: python -m world_engine_b200.csrc.build [--debug] [--verbose]
+Usage: python -m world_engine_b200.csrc.build [--debug] [--verbose] [-DNAME ...]
 """
 from __future__ import annotations
 
@@ -48,6 +48,7 @@ def build(debug: bool = False, verbose: bool = False, force: bool = False) -> st
         cmd += ["-Xptxas", "-v"]
     if debug:
         cmd += ["-DWE_ATTN_DEBUG"]
+    cmd += [a for a in sys.argv[1:] if a.startswith("-D")]
     cmd += [os.path.join(HERE, s) for s in SOURCES]
     cmd += ["-o", out]
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -144,7 +144,15 @@ __device__ __forceinline__ long long trace_clock() {
   do {                                                                                             \
     if (trace != nullptr) trace[(slot)] = static_cast<uint32_t>(val);                              \
   } while (0)
+// Stamps inside the single-thread issue loops lengthen the very chain they measure: they are compiled in only
+// on request (-DWE_ATTN_DEBUG_ISSUE).
+#ifdef WE_ATTN_DEBUG_ISSUE
+#define WE_TRACE_MMA(slot) WE_TRACE(slot)
 #else
+#define WE_TRACE_MMA(slot) do {} while (0)
+#endif
+#else
+#define WE_TRACE_MMA(slot) do {} while (0)
 #define WE_TRACE(slot) do {} while (0)
 #define WE_TRACE_VAL(slot, val) do {} while (0)
 #endif
@@ -408,7 +416,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     static_assert(kNumBars <= 32, "one lane per barrier");
     if (lane < kNumBars) {
       const int peers = p.nsplit > 1 ? p.nsplit - 1 : 1;
-      mbar_init(bars + lane, (lane >= 4 && lane < 8) ? kBlockM : (lane == 12 ? peers : 1));
+      mbar_init(bars + lane, (lane >= 4 && lane < 8) ? 4 : (lane == 12 ? peers : 1));   // p_ready: one arrival per warp
     }
     if (lane == 0) {
       prefetch_tensormap(&tm_k);
@@ -604,7 +612,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
           }
         }
-        if (is_k && a - nblind < 32) WE_TRACE(192 + a - nblind);
+        if (is_k && a - nblind < 32) WE_TRACE_MMA(192 + a - nblind);
         load_kv_tile(is_k, ring + st * Cfg::kTileBytes, &full[st], key_of(a));
       }
       if (storer) {
@@ -646,6 +654,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       constexpr uint32_t kTileStep = Cfg::kTileBytes >> 4;
       mbar_wait(q_full, 0, s_abort);
       // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; into S buffer i & 1.
+      // (The wait for the K tile stays right in front of the products: waiting for it a tile earlier, while the
+      // pipe is busy, was measured slower -- the K ring of 3 stages is not that far ahead under load.)
       auto issue_s = [&](int i) {
         const int a = load_seq(i);
         const int sk = a % kStagesK;
@@ -660,21 +670,22 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const uint32_t off = (kk >> 2) * kChunkStep + (kk & 3) * 2;          // 32 bytes per K step
           umma_ss_lo<1>(d, q_lo + off, kb + off, kIdescS);
         }
+        tc_commit(&s_ready[i & 1]);     // the softmax warps are waiting for this one
         tc_commit(&k_empty[sk]);
-        tc_commit(&s_ready[i & 1]);
       };
-      WE_TRACE(9);
+      WE_TRACE_MMA(9);
       issue_s(0);
-      WE_TRACE(10);
+      WE_TRACE_MMA(10);
       for (int i = 0; i < n; ++i) {
         const int av = load_seq(i);
         const int sv = av % kStagesV;
         const int buf = i & 1;
         // S(i+1) goes first: its buffer was released when both halves of P(i-1) were consumed, and the
         // tensor pipe computes it while the softmax warps are busy with S(i).
-        if (i < 8) WE_TRACE(96 + 6 * i);
+        if (i < 8) WE_TRACE_MMA(96 + 6 * i);
         if (i + 1 < n) issue_s(i + 1);
-        if (i < 8) WE_TRACE(97 + 6 * i);
+        if (i < 8) WE_TRACE_MMA(97 + 6 * i);
+        mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);   // landed long ago as a rule
         // O_g += P_g(i) V_g(i) for the two key halves g of the tile: M=128 queries, N=DH, K=64 keys in
         // steps of 16.  P_g sits in the first 32 columns of group g's half of S (two bf16 per column).
         const uint32_t vb = v_lo + sv * kTileStep;
@@ -685,8 +696,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (!(g_mode & 1))
 #endif
           mbar_wait(&p_ready[g * 2 + buf], (i >> 1) & 1, s_abort);
-          if (i < 8) WE_TRACE(98 + 6 * i + 2 * g);
-          if (g == 0) mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
+          if (i < 8) WE_TRACE_MMA(98 + 6 * i + 2 * g);
           tc_fence_after();
           const uint32_t d = tmem_base + kColO + 128u * g;
           const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
@@ -694,7 +704,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           for (int kk = 0; kk < 4; ++kk)                                          // 16 keys = 2048 bytes of V rows
             umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
           tc_commit(&o_ready[g]);
-          if (i < 8) WE_TRACE(99 + 6 * i + 2 * g);
+          if (i < 8) WE_TRACE_MMA(99 + 6 * i + 2 * g);
         }
         tc_commit(&v_empty[sv]);
       }
@@ -723,7 +733,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #ifdef WE_ATTN_DEBUG
       if (g_mode & 2) {   // experiment: no softmax work at all, only the hand-over
         if (i > 0) mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
-        mbar_arrive(&p_ready[wg * 2 + buf]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[wg * 2 + buf]);
         continue;
       }
 #endif
@@ -840,7 +851,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_st_wait();
       if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 6);
       tc_fence_before();
-      mbar_arrive(&p_ready[wg * 2 + buf]);
+      // one arrival per warp: 128 separate arrivals on one barrier word would queue up behind one another
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[wg * 2 + buf]);
       if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 7);
     }
 
