@@ -359,6 +359,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int q0 = qt * kBlockM;
   const uint8_t* wr = p.written + static_cast<int64_t>(b) * p.written_batch_stride;
 #ifdef WE_ATTN_DEBUG
+  const int dbg_mode = g_mode;   // read once: a global load inside the single-thread issue loop stalls the tensor pipe
   const long long t_start = trace_clock();
   uint32_t* trace = nullptr;
   {
@@ -693,7 +694,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
 #ifdef WE_ATTN_DEBUG
-          if (!(g_mode & 1))
+          if (!(dbg_mode & 1))
 #endif
           mbar_wait(&p_ready[g * 2 + buf], (i >> 1) & 1, s_abort);
           if (i < 8) WE_TRACE_MMA(98 + 6 * i + 2 * g);
@@ -731,7 +732,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
       if (row == 0 && i < 32) WE_TRACE(16 + 4 * i + 2 * wg);
 #ifdef WE_ATTN_DEBUG
-      if (g_mode & 2) {   // experiment: no softmax work at all, only the hand-over
+      if (dbg_mode & 2) {   // experiment: no softmax work at all, only the hand-over
         if (i > 0) mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
         __syncwarp();
         if (lane == 0) mbar_arrive(&p_ready[wg * 2 + buf]);
