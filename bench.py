@@ -43,7 +43,7 @@ N_LAYERS = 24
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu captures
 # summarised under profiles/ (bytes); None where no capture exists for that workload.
-NCU_TRAFFIC_BYTES = {"cfg2": 34.71e6, "cfg4": None, "cfg5": None}
+NCU_TRAFFIC_BYTES = {"cfg2": 34.71e6, "cfg3": 34.71e6, "cfg4": None, "cfg5": None}
 WORKLOAD = ("cfg2: B=1 H=16 Dh=128 T=256, 16-frame ring wrapped (frame_t=27, slot 11), bf16, append included; "
             "one step = 24 distinct layer caches (855 MB > L2, no flush needed)")
 
@@ -216,11 +216,15 @@ def run_ours(args):
             layers.append((slab.kv, slab._written.view(torch.uint8), slab.frame_t, 1))
         cache = None
     else:
-        cfg = CONFIGS[args.workload]
-        n_layers = N_LAYERS if args.workload == "cfg2" else 4
+        cfg = CONFIGS["cfg3_layer" if args.workload == "cfg3" else args.workload]
+        n_layers = N_LAYERS if args.workload in ("cfg2", "cfg3") else 4
         workload = WORKLOAD if args.workload == "cfg2" else (
             "cfg5: B=4 H=16 Dh=128 T=1024, 16-frame ring wrapped (16384 keys), bf16, append included; "
             "one step = 4 distinct layer caches (4 x 570 MB > L2)")
+        if args.workload == "cfg3":
+            workload = ("cfg3: one step = one generated frame of a 24-layer model at the cfg2 layer shape: 4 frozen "
+                        "denoise passes + 1 unfrozen pass that persists the frame = 120 layer-steps; the frame "
+                        "counter advances on the device after every frame, so the ring slot moves and wraps")
 
         class ModelCfg:   # the reference's config keys that size the cache (src/model/kv_cache.py:161-179)
             tokens_per_frame = cfg.T
@@ -251,9 +255,16 @@ def run_ours(args):
     v = torch.randn(shape_kv, device=dev, dtype=torch.bfloat16, generator=g)
     out = torch.empty_like(q)
 
+    # frozen flag of each pass over the layers within one step (src/world_engine.py:139-152 for cfg3)
+    passes = [True, True, True, True, False] if args.workload == "cfg3" else [True]
+
     def forward_layers():
-        for li, (kv, wr, ft, fts) in enumerate(layers):
-            ops.append_attend(q[li], k[li], v[li], kv, wr, ft, cfg.T, 1, True, 0.0, out=out[li], frame_t_stride=fts)
+        for frozen in passes:
+            for li, (kv, wr, ft, fts) in enumerate(layers):
+                ops.append_attend(q[li], k[li], v[li], kv, wr, ft, cfg.T, 1, frozen, 0.0, out=out[li],
+                                  frame_t_stride=fts)
+        if args.workload == "cfg3":
+            t_pos.add_(1)        # next frame: the device-resident frame counter all layers read
 
     def attention_only():
         for li, (kv, wr, ft, fts) in enumerate(layers):
@@ -308,9 +319,9 @@ def run_ours(args):
     if args.profile:
         if rank == 0:
             print(json.dumps({"profile_run": True, "workload": args.workload,
-                              "us_per_layer_step": ms * 1e3 / (n_layers * args.steps),
+                              "us_per_layer_step": ms * 1e3 / (n_layers * len(passes) * args.steps),
                               "attn_us_per_launch": attn_us,
-                              "tflops": cfg.flops() / (ms * 1e-3 / (n_layers * args.steps)) / 1e12}))
+                              "tflops": cfg.flops() / (ms * 1e-3 / (n_layers * len(passes) * args.steps)) / 1e12}))
         if world > 1:
             dist.destroy_process_group()
         return 0
@@ -324,13 +335,21 @@ def run_ours(args):
         dq.copy_(hq, non_blocking=True)
         dk.copy_(hk, non_blocking=True)
         dv.copy_(hv, non_blocking=True)
-        for li in range(n_layers):
-            if cache is not None:     # public API of the layer caches
-                y = cache.append_and_attend(dq[li], dk[li], dv[li], pos, li)
-            else:                     # public API of the session slab
-                kv, wr, ft, fts = layers[li]
-                y = ops.append_attend(dq[li], dk[li], dv[li], kv, wr, ft, cfg.T, 1, True, 0.0, frame_t_stride=fts)
-            hout[li].copy_(y, non_blocking=True)
+        for pi, frozen in enumerate(passes):
+            if pi > 0:
+                dq.copy_(hq, non_blocking=True)       # every denoise pass brings new queries
+            if cache is not None:
+                cache.set_frozen(frozen)
+            for li in range(n_layers):
+                if cache is not None:     # public API of the layer caches
+                    y = cache.append_and_attend(dq[li], dk[li], dv[li], pos, li)
+                else:                     # public API of the session slab
+                    kv, wr, ft, fts = layers[li]
+                    y = ops.append_attend(dq[li], dk[li], dv[li], kv, wr, ft, cfg.T, 1, frozen, 0.0,
+                                          frame_t_stride=fts)
+                hout[li].copy_(y, non_blocking=True)
+        if args.workload == "cfg3":
+            t_pos.add_(1)
         torch.cuda.synchronize()
         return float(hout[0, 0, 0, 0, 0])
 
@@ -342,8 +361,8 @@ def run_ours(args):
         e2e_step()
     barrier()
     e2e_s = time.perf_counter() - t0
-    h2d = (hq.numel() + hk.numel() + hv.numel()) * 2
-    d2h = hout.numel() * 2
+    h2d = (len(passes) * hq.numel() + hk.numel() + hv.numel()) * 2
+    d2h = len(passes) * hout.numel() * 2
 
     # max over ranks
     times = torch.tensor([ms, e2e_s * 1e3, attn_us], device=dev, dtype=torch.float64)
@@ -353,9 +372,9 @@ def run_ours(args):
 
     if rank == 0:
         hbm_peak, tc_peak, peak_kind = measured_peaks()
-        total_layer_steps = world * n_layers * args.steps
+        total_layer_steps = world * n_layers * len(passes) * args.steps
         value = total_layer_steps / (ms * 1e-3)
-        us_per_layer_step = ms * 1e3 / (n_layers * args.steps)
+        us_per_layer_step = ms * 1e3 / (n_layers * len(passes) * args.steps)
         elem = 2
         attn_bytes = cfg.B * (2 * cfg.Hkv * cfg.visible_keys() * cfg.Dh * elem + 2 * cfg.Hq * cfg.T * cfg.Dh * elem)
         # the slower of HBM time and tensor time bounds the kernel (measured peaks)
@@ -378,11 +397,12 @@ def run_ours(args):
             "metric": "frame-attn layer-steps/s (append + attention)", "value": value, "unit": "layer-steps/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload, "layer_steps_per_step": n_layers, "sessions_per_gpu": cfg.B,
+            "config": {"workload": workload, "layer_steps_per_step": n_layers * len(passes), "sessions_per_gpu": cfg.B,
                        "l2": "inputs larger than L2 (distinct caches cycled within a step)"},
             "us_per_layer_step": us_per_layer_step,
             "tflops": cfg.flops() / (us_per_layer_step * 1e-6) / 1e12,
             "sessions_frames_per_s": value * cfg.B / (24 * 5) if args.workload == "cfg4" else value / (24 * 5),
+            "us_per_frame": (ms * 1e3 / args.steps) if args.workload == "cfg3" else None,
             "roofline": roof,
             "cpu_baseline": cpu,
             "e2e": {"value": total_layer_steps / (e2e_ms * 1e-3), "unit": "layer-steps/s",
@@ -402,8 +422,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["cfg2", "cfg4", "cfg5"], default="cfg2",
-                    help="cfg2 (default, the headline layer-step); cfg4 = 64 sessions with 32-frame rings batched in "
+    ap.add_argument("--workload", choices=["cfg2", "cfg3", "cfg4", "cfg5"], default="cfg2",
+                    help="cfg2 (default, the headline layer-step); cfg3 = whole frames of a 24-layer model (4 frozen passes + 1 "
+                         "persisting pass, frame counter advancing on the device); cfg4 = 64 sessions with 32-frame rings batched in "
                          "one launch per layer-step; cfg5 = B=4, 1024 tokens per frame, 16384 keys")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed legs only (skips the end-to-end and CPU-baseline legs): for runs under ncu")

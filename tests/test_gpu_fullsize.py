@@ -87,3 +87,38 @@ def test_properties_at_full_size():
     shifted = cache_b.append_and_attend(qd, kd, vd, gh.pos_ids(cfg_b, t + 1), True).float()
     assert (shifted - base).abs().max().item() <= 8e-3      # only the summation order differs
     ops.check_status(torch.device("cuda"))
+
+
+def test_denoise_protocol_over_twenty_frames_at_layer_size():
+    """The call sequence of WorldEngine._denoise_pass / _cache_pass (src/world_engine.py:139-152) on one layer
+    cache of the cfg3 shape: per frame four frozen steps, then one unfrozen step that persists the frame, for
+    21 consecutive frames, so every ring slot is overwritten at least once.  The cache must equal the oracle's
+    after every frame; the attention of the last frozen step and of the persisting step of selected frames is
+    compared on a subset of rows and heads."""
+    cfg = CONFIGS["cfg3_layer"]
+    cache, ocache = _fill(cfg)
+    rows = sorted({r % cfg.T for r in ROWS})
+    heads = sorted({0, cfg.Hq // 2, cfg.Hq - 1})
+    checked = {cfg.frame_t, cfg.frame_t + 7, cfg.frame_t + 20}
+    for t in range(cfg.frame_t, cfg.frame_t + 21):
+        _, k, v = helpers.step_inputs(cfg, t, 0)          # K/V of a frame are the same at every step of it
+        kd, vd = gh.dev_tensor(cfg, k), gh.dev_tensor(cfg, v)
+        kv_new = np.stack([helpers.to_container(cfg, k), helpers.to_container(cfg, v)], 0)
+        pos = gh.pos_ids(cfg, t)
+        for step in range(5):
+            frozen = step < 4
+            q = frame_q(cfg, t, step)
+            q = oracle.round_to_bf16(q)
+            out = cache.append_and_attend(gh.dev_tensor(cfg, q), kd, vd, pos, frozen)
+            k_full, v_full, mask = ocache.upsert(kv_new, t, frozen)
+            if t in checked and step >= 3:
+                assert int(mask.sum()) == cfg.visible_keys()
+                kf = helpers.from_container(cfg, k_full[:1, [h * cfg.Hkv // cfg.Hq for h in heads]])
+                vf = helpers.from_container(cfg, v_full[:1, [h * cfg.Hkv // cfg.Hq for h in heads]])
+                want = oracle.frame_attention(q[:1][:, heads][:, :, rows], kf, vf, mask)
+                got = out[:1][:, heads][:, :, rows].float().cpu().numpy()
+                mx, mean = helpers.error_stats(got, want)
+                assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"frame {t} step {step}: {mx} {mean}"
+        assert gh.kv_bytes(cache) == ocache.kv.tobytes(), f"cache differs after frame {t}"
+        assert np.array_equal(cache.written.cpu().numpy(), ocache.written)
+    ops.check_status(torch.device("cuda"))
