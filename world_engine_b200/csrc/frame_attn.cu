@@ -19,7 +19,8 @@
 //               are in-thread reductions.  Group g handles keys [64g, 64g+64)
 //               of every tile as a stream of its own: running maximum, row
 //               sum and accumulator O_g; the two streams are merged once at
-//               the end.  exp2 with the scale folded in; the running maximum
+//               the end.  exp2 with the scale folded in (packed fp32 pairs for the
+//               arithmetic, ex2.approx per element); the running maximum
 //               is raised (and O_g rescaled in tensor memory) only when it
 //               grew by more than 2^8; P (bf16/f16) overwrites the S columns
 //               the thread has consumed.
@@ -148,10 +149,13 @@ __device__ __forceinline__ long long trace_clock() {
 // on request (-DWE_ATTN_DEBUG_ISSUE).
 #ifdef WE_ATTN_DEBUG_ISSUE
 #define WE_TRACE_MMA(slot) WE_TRACE(slot)
+constexpr bool kFullTrace = true;
 #else
+constexpr bool kFullTrace = false;     // per-tile stamps of the softmax warps too only on request: they cost time
 #define WE_TRACE_MMA(slot) do {} while (0)
 #endif
 #else
+constexpr bool kFullTrace = false;
 #define WE_TRACE_MMA(slot) do {} while (0)
 #define WE_TRACE(slot) do {} while (0)
 #define WE_TRACE_VAL(slot, val) do {} while (0)
@@ -691,21 +695,23 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // steps of 16.  P_g sits in the first 32 columns of group g's half of S (two bf16 per column).
         const uint32_t vb = v_lo + sv * kTileStep;
         const uint32_t acc0 = i > 0 ? 1u : 0u;
+#ifdef WE_ATTN_DEBUG
+        if (!(dbg_mode & 1))
+#endif
+        {
+          mbar_wait(&p_ready[0 * 2 + buf], (i >> 1) & 1, s_abort);
+          mbar_wait(&p_ready[1 * 2 + buf], (i >> 1) & 1, s_abort);
+        }
+        tc_fence_after();
+        // one burst of eight products: every wait, fence or commit between two products is a bubble in the pipe
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-#ifdef WE_ATTN_DEBUG
-          if (!(dbg_mode & 1))
-#endif
-          mbar_wait(&p_ready[g * 2 + buf], (i >> 1) & 1, s_abort);
-          if (i < 8) WE_TRACE_MMA(98 + 6 * i + 2 * g);
-          tc_fence_after();
           const uint32_t d = tmem_base + kColO + 128u * g;
           const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)                                          // 16 keys = 2048 bytes of V rows
             umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
           tc_commit(&o_ready[g]);
-          if (i < 8) WE_TRACE_MMA(99 + 6 * i + 2 * g);
         }
         tc_commit(&v_empty[sv]);
       }
@@ -730,7 +736,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
       mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
-      if (row == 0 && i < 32) WE_TRACE(16 + 4 * i + 2 * wg);
+      if (row == 0 && i < 32 && (kFullTrace || i == 1 || i == n - 1)) WE_TRACE(16 + 4 * i + 2 * wg);
 #ifdef WE_ATTN_DEBUG
       if (dbg_mode & 2) {   // experiment: no softmax work at all, only the hand-over
         if (i > 0) mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
@@ -744,7 +750,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_ld32(s_addr, s[0]);
       tmem_ld32(s_addr + 32, s[1]);
       tmem_ld_wait();
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 0);
+      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 0);
       const uint32_t entry = s_list[t0 + i];
       if (entry & 1u) {
         // partial tile: mask tokens that are unwritten, hidden, or beyond the buffer
@@ -779,40 +785,21 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         l_run *= alpha;
         m_run = m_new;
       }
-      // P = exp2(S * scale - m) on packed pairs.  The special-function unit does 16 exponentials per clock and
-      // SM and is the scarcest resource here, so 13 of the 32 pairs take a software path on the FMA pipe
-      // instead: round-to-nearest split x = r + f by the magic-number add, a degree-3 polynomial for 2^f on
-      // [-0.5, 0.5] (relative error 7.5e-5, far below the bf16 resolution of P), and r added into the exponent.
+      // P = exp2(S * scale - m): the argument on packed fp32 pairs (one FMA per pair), one ex2.approx per element.
+      // Measured alternatives, all slower with the packed arithmetic in place: a share of the exponentials as
+      // a cubic polynomial on the FMA pipe (costs more issue slots than it frees on the special-function pipe;
+      // 13 of 32 pairs: +3 %), ex2 on packed bf16 pairs (+5 %, and twice the error).
       const uint64_t scale2 = splat2(p.scale_log2), negm2 = splat2(-m_run);
-      const uint64_t magic2 = splat2(12582912.f), negmagic2 = splat2(-12582912.f), minus1_2 = splat2(-1.f);
-      const uint64_t c0_2 = splat2(0.9999281168f), c1_2 = splat2(0.6932609677f);
-      const uint64_t c2_2 = splat2(0.2426105440f), c3_2 = splat2(0.0551713258f);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t pk[32];
 #pragma unroll
       for (int q = 0; q < 32; ++q) {
         const int c = q >> 4, e = q & 15;
         const uint64_t x2 = fma2(pk64(s[c][2 * e], s[c][2 * e + 1]), scale2, negm2);
-        uint32_t xl, xh, pl, ph;
+        uint32_t xl, xh;
         upk64(x2, xl, xh);
-        if ((q % 5) == 1 || (q % 5) == 3) {
-          const uint64_t xc2 = pk64(__float_as_uint(fmaxf(__uint_as_float(xl), -125.f)),
-                                    __float_as_uint(fmaxf(__uint_as_float(xh), -125.f)));
-          const uint64_t t2 = add2(xc2, magic2);            // low mantissa bits = round(x)
-          const uint64_t r2 = add2(t2, negmagic2);          // round(x) as a float
-          const uint64_t f2 = fma2(r2, minus1_2, xc2);      // x - round(x) in [-0.5, 0.5]
-          uint64_t p2 = fma2(f2, c3_2, c2_2);
-          p2 = fma2(p2, f2, c1_2);
-          p2 = fma2(p2, f2, c0_2);
-          uint32_t tl, th, ql, qh;
-          upk64(t2, tl, th);
-          upk64(p2, ql, qh);
-          pl = ql + (tl << 23);                             // 2^f * 2^round(x)
-          ph = qh + (th << 23);
-        } else {
-          pl = __float_as_uint(fast_exp2(__uint_as_float(xl)));
-          ph = __float_as_uint(fast_exp2(__uint_as_float(xh)));
-        }
+        const uint32_t pl = __float_as_uint(fast_exp2(__uint_as_float(xl)));
+        const uint32_t ph = __float_as_uint(fast_exp2(__uint_as_float(xh)));
         sum2[q & 3] = add2(sum2[q & 3], pk64(pl, ph));
         pk[q] = pack2<BF16>(__uint_as_float(pl), __uint_as_float(ph));
       }
@@ -829,13 +816,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tmem_st32(s_addr, pk);                                    // P over the S columns this thread has consumed
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      if (row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
+      if (kFullTrace && row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
       if (i > 0) {
         // PV_g(i-1) has long been issued; its completion makes O_g safe to touch and is awaited every tile so
         // that no phase of the barrier is ever skipped.
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 4);
+      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 4);
         mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 5);
+      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 5);
         if (raise) {
           tc_fence_after();
 #pragma unroll 1
@@ -850,12 +837,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       tmem_st_wait();
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 6);
+      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 6);
       tc_fence_before();
       // one arrival per warp: 128 separate arrivals on one barrier word would queue up behind one another
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[wg * 2 + buf]);
-      if (row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 7);
+      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 7);
     }
 
     // ---------------------------------------------------------- after the last tile
