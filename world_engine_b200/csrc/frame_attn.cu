@@ -1044,7 +1044,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // CTA `split` of the cluster produces rows [r0, r1) of the query tile.  Every CTA pushes, with one bulk
   // copy per peer, the (already weighted) rows that peer owns into the peer's receive buffer (the idle V
   // ring); the owner adds its own rows and the received ones in split order, so reruns are bit-identical.
-  if (p.cluster_merge && p.nsplit > 1) {
+  if (p.cluster_merge && p.nsplit > 1 && warp < 8) {
+    // Only the 256 threads that staged the rows take part: a barrier among them, not the whole CTA.
     const int ns = p.nsplit;
     const int r0 = (kBlockM * split) / ns, r1 = (kBlockM * (split + 1)) / ns;
     const int R = r1 - r0;
@@ -1052,16 +1053,16 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     float* recv = reinterpret_cast<float*>(sV);
     const int slot_floats = R * Cfg::kPartRow;
     if (lane == 0) WE_TRACE(244 + warp);
-    __syncthreads();                  // this CTA's rows are staged
-    // One courier thread per peer (the last of the threads that share row `peer`, which has the fewest columns
-    // to sum later) sends that peer its rows and, once this CTA's own inbox is full, the acknowledgement.
-    const int tpr = kAttnThreads / R;            // threads per row in the sum below
+    named_bar_sync(1, kSoftmaxThreads);           // this CTA's rows are staged
+    // One courier thread per peer (lane 0 of warp `peer`) sends that peer its rows and, once this CTA's own
+    // inbox is full, the acknowledgement.
+    const int tpr = kSoftmaxThreads / R;          // threads per row in the sum below (2 ns)
     const int rl = tid / tpr;
     const int cg0 = tid - rl * tpr;
-    const bool courier = cg0 == tpr - 1 && rl < ns && rl != split;
+    const bool courier = lane == 0 && warp < ns && warp != split;
     if (tid == 0) WE_TRACE(236);
     if (courier) {
-      const int d = rl;
+      const int d = warp;
       // once all peers' pairs are here their main loops are over, so their V rings may be written
       mbar_wait(ml_bar, 0, s_abort);
       const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
@@ -1076,14 +1077,16 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // copy: the ordinary wait of the receiving CTA orders the data)
     mbar_wait(ml_bar, 0, s_abort);           // all pairs present
     if (tid == 0) WE_TRACE(242);
-    // 3 * ns threads share one of the R = 128 / ns rows; each takes every (3 ns)-th group of 4 columns.  Split
+    // 2 * ns threads share one of the R = 128 / ns rows; each takes every (2 ns)-th group of 4 columns (eight
+    // neighbouring lanes read one 128-byte line: no bank conflicts).  Split
     // u's row enters with the weight exp2(m_u - m_row) / l_row, l_row = sum over splits of l_u exp2(m_u - m_row),
     // computed once per thread.  Compiled once per split count, so that no loop carries dead iterations.
     auto sum_rows = [&](auto ns_const) {
       constexpr int NS = decltype(ns_const)::value;
       constexpr int kGroups = DH / 4;
-      constexpr int kTpr = 3 * NS;                                  // = kAttnThreads / (kBlockM / NS)
-      constexpr int kMaxIt = (kGroups + kTpr - 1) / kTpr;
+      constexpr int kTpr = 2 * NS;                                  // = kSoftmaxThreads / (kBlockM / NS)
+      constexpr int kMaxIt = kGroups / kTpr;
+      static_assert(kGroups % kTpr == 0, "every thread takes the same number of column groups");
       const int row = r0 + rl;
       float w_u[NS], l_u[NS];
       float m_all = -INFINITY;
@@ -1107,7 +1110,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(recv_bar, 0, s_abort);         // the rows of all peers have landed
       if (tid == 0) WE_TRACE(237);
       // acknowledge to the sender: its staging buffer is no longer read
-      if (courier) mbar_arrive_remote(dsmem_addr(smem_u32(ack_bar), static_cast<uint32_t>(rl)));
+      if (courier) mbar_arrive_remote(dsmem_addr(smem_u32(ack_bar), static_cast<uint32_t>(warp)));
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2]);
       const bool in_range = q0 + row < p.T;
@@ -1123,7 +1126,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int k = 0; k < kMaxIt; ++k) {
           const int cg = cg0 + k * kTpr;
-          if ((k + 1) * kTpr <= kGroups || cg < kGroups) {
+          {
             const float4 v = *reinterpret_cast<const float4*>(src + cg * 4);
             acc[k].x = fmaf(w, v.x, acc[k].x);
             acc[k].y = fmaf(w, v.y, acc[k].y);
@@ -1137,7 +1140,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int k = 0; k < kMaxIt; ++k) {
           const int cg = cg0 + k * kTpr;
-          if ((k + 1) * kTpr <= kGroups || cg < kGroups) {
+          {
             uint2 v2;
             v2.x = pack2<BF16>(acc[k].x, acc[k].y);
             v2.y = pack2<BF16>(acc[k].z, acc[k].w);
