@@ -424,8 +424,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(bars + lane, (lane >= 4 && lane < 8) ? 4 : (lane == 12 ? peers : 1));   // p_ready: one arrival per warp
     }
     if (lane == 0) {
-      prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_q);
+      prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
       if (p.fused) {
         prefetch_tensormap(&tm_kn);
@@ -458,6 +458,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   grid_dependency_wait();
   if (tid == 0) WE_TRACE(5);
   const int64_t ft = p.frame_t[static_cast<int64_t>(b) * p.frame_t_stride];
+  if (warp == 8 && lane == 0) {
+    // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.  It does not depend on the frame
+    // counter, so it goes out while that load is in flight.
+    mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
+    const int x1 = pick3(p.q_perm[0], q0, h, b), x2 = pick3(p.q_perm[1], q0, h, b), x3 = pick3(p.q_perm[2], q0, h, b);
+#pragma unroll
+    for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, x1, x2, x3);
+  }
   // Candidate tiles = physical tiles minus those that lie entirely in the hidden slot (pure arithmetic on
   // the frame counter).  Split `split` owns candidates [c0, c1); which of them hold a visible key is decided
   // below from `written`.
@@ -483,16 +491,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (stid & 7) : 0x3FFFFFF, p.C);
   if (warp == 8 && lane == 0) {
     // The first tiles of the range, before it is known whether they hold a visible key (they almost always
-    // do; a miss is drained later): DRAM latency then overlaps the rest of the set-up and the scan.  K(0) and
-    // Q, which the first product needs, go first.
+    // do; a miss is drained later): DRAM latency then overlaps the rest of the set-up and the scan.  K(0),
+    // which the first product needs, goes first.
     if (nblind > 0) load_kv_tile(true, sK, &k_full[0], phys_tile(c0) * kBlockN);
-    {
-      // Q tile: rows q0 .. q0+127 of (b, h); rows past T are zero-filled by TMA.
-      mbar_arrive_expect_tx(q_full, Cfg::kTileBytes);
-      const int x1 = pick3(p.q_perm[0], q0, h, b), x2 = pick3(p.q_perm[1], q0, h, b), x3 = pick3(p.q_perm[2], q0, h, b);
-#pragma unroll
-      for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, x1, x2, x3);
-    }
     if (nblind > 0) load_kv_tile(false, sV, &v_full[0], phys_tile(c0) * kBlockN);
     for (int j = 1; j < nblind; ++j) {
       const int key0 = phys_tile(c0 + j) * kBlockN;
