@@ -1,7 +1,7 @@
 """Generates the golden fixtures of this directory by RUNNING THE REFERENCE.
 
-Runs only where the reference tree is mounted (REFERENCE_ROOT, default
-/root/reference): it imports the reference's own `src/model/kv_cache.py`
+Runs only where a checkout of the reference is available (its location is
+taken from the environment variable REFERENCE_ROOT): it imports the reference's own `src/model/kv_cache.py`
 (LayerKVCache.upsert, make_block_mask) by path and calls torch's un-compiled
 `flex_attention` exactly as `src/model/attn.py:116` does, on the seeded inputs
 of `world_engine_b200.synthetic`.  The reference publishes no tests or golden
@@ -11,7 +11,8 @@ vectors for this path, so these recorded outputs are what pins the oracle.
 installed; a stub module providing `TensorDict = dict` is injected.  Nothing
 from the reference is copied into the repository: only its OUTPUTS are stored.
 
-Usage:  python tests/golden/make_golden.py            (rewrites tests/golden/*.npz)
+Usage:  REFERENCE_ROOT=<checkout of the reference> python tests/golden/make_golden.py
+        (rewrites tests/golden/*.npz)
 """
 from __future__ import annotations
 
@@ -33,7 +34,9 @@ sys.path.insert(0, ROOT)
 from world_engine_b200 import synthetic  # noqa: E402
 from world_engine_b200.synthetic import StepConfig  # noqa: E402
 
-REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("REFERENCE_ROOT", "")
+if not os.path.isdir(os.path.join(REFERENCE_ROOT, "src", "model")):
+    raise SystemExit("make_golden.py: set REFERENCE_ROOT to a checkout of the reference (it needs src/model/kv_cache.py)")
 
 
 def load_reference_kv_cache():

@@ -89,7 +89,7 @@ struct AttnCfg {
   static constexpr int kSmemAux = 64 * 8 + kMaxTiles * 2 + 64 + 4 * kBlockM * 4 + kMaxTiles + 8 * kBlockM * 8;
   static constexpr int kSmemBytes = kSmemTiles + kSmemAux + 1024;  // + slack for 1024-byte alignment
   // Exchange buffers of the epilogue, laid over the (then idle) rings: the CTA's partial O tile
-  // [128][DH + 4] fp32 over the K ring (row maximum and row sum in the first two pad columns), and the
+  // [128][DH + 4] fp32 over the K ring (4 pad columns keep the row stride off a multiple of 128 bytes), and the
   // rows received from the other splits over the V ring.
   static constexpr int kPartRow = DH + 4;
   static constexpr int kPartFloats = kBlockM * kPartRow;
@@ -1043,8 +1043,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   // ------------------------------------------------ merge of the splits through cluster shared memory
   // CTA `split` of the cluster produces rows [r0, r1) of the query tile.  Every CTA pushes, with one bulk
-  // copy per peer, the (already weighted) rows that peer owns into the peer's receive buffer (the idle V
-  // ring); the owner adds its own rows and the received ones in split order, so reruns are bit-identical.
+  // copy per peer, the rows that peer owns (un-normalised, relative to this split's maximum) into the peer's
+  // receive buffer (the idle V ring); the owner weights and adds its own rows and the received ones in split
+  // order, so reruns are bit-identical.
   if (p.cluster_merge && p.nsplit > 1 && warp < 8) {
     // Only the 256 threads that staged the rows take part: a barrier among them, not the whole CTA.
     const int ns = p.nsplit;
