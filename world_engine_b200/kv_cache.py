@@ -108,7 +108,8 @@ class B200LayerKVCache(nn.Module):
     def append_and_attend(self, q: Tensor, k: Tensor, v: Tensor, pos_ids: Mapping[str, Tensor],
                           is_frozen: bool, scale: float = 0.0) -> Tensor:
         """Append the frame and attend to the cache: what upsert + flex_attention
-        do at src/model/attn.py:113-116, in two launches and no BlockMask."""
+        do at src/model/attn.py:113-116, without a BlockMask (one launch when the
+        tail frame is made of whole 128-key tiles, else append + attention)."""
         t_pos = self._frame_t(pos_ids)
         self._check(k, t_pos)
         return ops.append_attend_op(q, k, v, self.kv, self.written.view(torch.uint8), t_pos,
