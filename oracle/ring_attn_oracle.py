@@ -199,3 +199,65 @@ def frame_step(cache: OracleLayerKVCache, q_f32: np.ndarray, kv_new: np.ndarray,
     """
     k_full, v_full, mask = cache.upsert(kv_new, frame_t, is_frozen)
     return frame_attention(q_f32, to_f32(k_full), to_f32(v_full), mask, scale)
+
+
+# --------------------------------------------------------------------------
+# what happens to q, k, v between the projections and the cache
+# (src/model/attn.py:105-110, src/patch_model.py:124-129)
+# --------------------------------------------------------------------------
+F32_EPS = float(np.finfo(np.float32).eps)
+
+
+def unit_rms_norm(x_f32: np.ndarray, eps: float = F32_EPS) -> np.ndarray:
+    """Weightless RMS norm over the last axis in fp32: x * rsqrt(mean(x^2) + eps)
+    (`rms_norm`, src/model/nn.py:55-56: F.rms_norm without weight and with the
+    default eps, which for 16-bit inputs is the fp32 machine epsilon because the
+    op computes in fp32).  The caller rounds the result to the tensor's dtype."""
+    x = np.asarray(x_f32, dtype=np.float32)
+    ms = np.mean(x * x, axis=-1, keepdims=True, dtype=np.float32)
+    return (x * (np.float32(1.0) / np.sqrt(ms + np.float32(eps)))).astype(np.float32)
+
+
+def rope_rotate(x_f32: np.ndarray, cos: np.ndarray, sin: np.ndarray) -> np.ndarray:
+    """RoPE.forward (src/model/attn.py:33-40) in fp32: consecutive pairs
+    (x[2j], x[2j+1]) are rotated by the angle j of the token and the result is
+    laid out as [all first components | all second components].
+    x [..., T, Dh]; cos, sin [..., T, Dh/2] (broadcast over heads by the caller)."""
+    x = np.asarray(x_f32, dtype=np.float32)
+    x0, x1 = x[..., 0::2], x[..., 1::2]
+    c, s = np.asarray(cos, dtype=np.float32), np.asarray(sin, dtype=np.float32)
+    y0 = (x0 * c).astype(np.float32) - (x1 * s).astype(np.float32)
+    y1 = (x1 * c).astype(np.float32) + (x0 * s).astype(np.float32)
+    return np.concatenate([y0, y1], axis=-1).astype(np.float32)
+
+
+def rope_angles(cos_table: np.ndarray, sin_table: np.ndarray, t_pos, y_pos, x_pos, height: int, width: int):
+    """RoPE.get_angles (src/model/attn.py:22-31): row t*(H*W) + y*W + x of the
+    tables for every token; returns cos, sin [B, 1, T, Dh/2]."""
+    flat = np.asarray(t_pos, dtype=np.int64) * (height * width) + np.asarray(y_pos, dtype=np.int64) * width \
+        + np.asarray(x_pos, dtype=np.int64)
+    if flat.min() < 0 or flat.max() >= cos_table.shape[0]:
+        raise IndexError("position outside the RoPE table")
+    return cos_table[flat][:, None], sin_table[flat][:, None]
+
+
+def value_residual(v_f32: np.ndarray, v1_f32: np.ndarray, lamb: float) -> np.ndarray:
+    """torch.lerp(v, v1, lamb) in fp32 (src/model/attn.py:105-107), with the
+    two-sided form torch uses: start + w*diff below 0.5, end - diff*(1-w) from 0.5 on."""
+    v = np.asarray(v_f32, dtype=np.float32)
+    d = np.asarray(v1_f32, dtype=np.float32) - v
+    w = np.float32(lamb)
+    if abs(float(lamb)) < 0.5:
+        return (v + w * d).astype(np.float32)
+    return (np.asarray(v1_f32, dtype=np.float32) - d * (np.float32(1.0) - w)).astype(np.float32)
+
+
+def qkv_prologue(q, k, v, v1, lamb, cos, sin, rounder=round_to_bf16):
+    """q, k, v [B,H,T,Dh] fp32 values of 16-bit tensors -> (q', k', v') as the
+    attention and the cache receive them: v' = lerp(v, v1, lamb) (skipped when
+    v1 is None), q' = rope(rms_norm(q)), k' = rope(rms_norm(k)); `rounder`
+    rounds to the tensors' dtype after every step that materialises a tensor in
+    the reference (the norm, the rotation, the lerp)."""
+    vo = np.asarray(v, dtype=np.float32) if v1 is None else rounder(value_residual(v, v1, lamb))
+    qn, kn = rounder(unit_rms_norm(q)), rounder(unit_rms_norm(k))
+    return rounder(rope_rotate(qn, cos, sin)), rounder(rope_rotate(kn, cos, sin)), vo
