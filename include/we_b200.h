@@ -75,7 +75,8 @@ enum {
 /* Device status codes written to *status by the attention kernel. */
 enum {
   WE_B200_ST_OK = 0,
-  WE_B200_ST_WAIT_EXPIRED = 1  /* a bounded mbarrier wait gave up; output invalid */
+  WE_B200_ST_WAIT_EXPIRED = 1, /* a bounded mbarrier wait gave up; output invalid */
+  WE_B200_ST_INDEX_RANGE = 2   /* a token position points outside the RoPE table (the row was clamped) */
 };
 
 typedef struct we_b200_cache_geom {
@@ -197,6 +198,43 @@ WE_B200_API int we_b200_frame_attn_static(const void* q, const int64_t* q_stride
                               const void* kv, const uint8_t* written, const int64_t* frame_t,
                               const we_b200_cache_geom* geom_host, float scale,
                               int32_t* status, void* stream);
+
+/*
+ * What happens to q, k, v between the projections and the cache, in one pass
+ * (next to the hot path: src/model/attn.py:105-110, src/patch_model.py:124-129):
+ *   v'  = lerp(v, v1, v_lamb)                 if v1 != NULL     (torch.lerp, :105-107)
+ *   q'  = rope(rms_norm(q)),  k' = rope(rms_norm(k))            (:109-110)
+ * rms_norm is the weightless F.rms_norm over the head dim computed in fp32
+ * (src/model/nn.py:55-56) and rounded to the tensor dtype; rope is RoPE.forward
+ * (src/model/attn.py:33-40): consecutive pairs rotated in fp32 by the angles of
+ * table row t*(height*width) + y*width + x (get_angles, :22-31), output laid
+ * out as [first components | second components].  All tensors are [B,H,T,Dh]
+ * views with strides (b,h,t) in elements, head dim contiguous; outputs may
+ * alias nothing but their own input.  A position outside the table sets
+ * *status to WE_B200_ST_INDEX_RANGE (the reference's index_select would raise).
+ */
+typedef struct we_b200_prologue_args {
+  const void* q_in;  const void* k_in;  const void* v_in;
+  const void* v1;                       /* value-residual source, or NULL        */
+  void* q_out;  void* k_out;  void* v_out;
+  int64_t q_in_strides[3], k_in_strides[3], v_in_strides[3], v1_strides[3];
+  int64_t q_out_strides[3], k_out_strides[3], v_out_strides[3];
+  const void* v_lamb;                   /* device scalar, dtype v_lamb_dtype      */
+  int32_t v_lamb_dtype;                 /* WE_B200_BF16 / F16 / F32               */
+  const float* cos_table;               /* [table_rows][Dh/2] fp32                */
+  const float* sin_table;
+  int64_t table_rows;
+  const int64_t* t_pos;                 /* [B][T] int64, rows pos_batch_stride apart */
+  const int64_t* y_pos;
+  const int64_t* x_pos;
+  int64_t pos_batch_stride;
+  int32_t height, width;                /* latent grid of the position ids        */
+  int32_t B, T, Hq, Hkv, Dh;
+  int32_t dtype;                        /* WE_B200_BF16 or WE_B200_F16            */
+  float eps;                            /* of the RMS norm (fp32 epsilon by default in the reference) */
+} we_b200_prologue_args;
+
+WE_B200_API int we_b200_qkv_prologue(const we_b200_prologue_args* args_host, int32_t* status, void* stream);
 
 /* Number of kernels the previous three entry points have launched in this
  * process (diagnostic counter for benchmarks; relaxed atomics). */

@@ -135,3 +135,63 @@ def test_module_forward_matches_fp32_restatement():
         assert err.max().item() <= 3e-2 and err.mean().item() <= 3e-3, (t, frozen, err.max().item(), err.mean().item())
         # (the projections run in cuBLAS on the GPU and in fp32 here, so the cached K/V agree only to bf16 rounding)
         assert torch.equal(cache.layers[0].written.cpu(), torch.from_numpy(ocache.written))
+
+
+class _TableRope(nn.Module):
+    """Table form of RoPE with the reference's forward (src/model/attn.py:12-40): `cos` / `sin` buffers indexed
+    by t*(H*W) + y*W + x; the table values are seeded here (their generation is a third-party package's)."""
+
+    def __init__(self, height, width, frames, d_head):
+        super().__init__()
+        self.config = type("C", (), {"height": height, "width": width})()
+        g = torch.Generator().manual_seed(11)
+        ang = torch.rand(frames * height * width, d_head // 2, generator=g) * 6.28 - 3.14
+        self.cos = nn.Buffer(ang.cos().contiguous(), persistent=False)
+        self.sin = nn.Buffer(ang.sin().contiguous(), persistent=False)
+
+    def forward(self, x, pos_ids):
+        t, y, xx = pos_ids["t_pos"], pos_ids["y_pos"], pos_ids["x_pos"]
+        flat = (t * (self.config.height * self.config.width) + y * self.config.width + xx).reshape(-1)
+        cos = self.cos.index_select(0, flat).view(*t.shape, -1)[:, None]
+        sin = self.sin.index_select(0, flat).view(*t.shape, -1)[:, None]
+        x0, x1 = x.float().unfold(-1, 2, 2).unbind(-1)
+        return torch.cat((x0 * cos - x1 * sin, x1 * cos + x0 * sin), dim=-1).type_as(x)
+
+
+@pytest.mark.gpu
+def test_module_with_table_rope_uses_the_one_pass_prologue_and_agrees_with_the_torch_ops():
+    """Same module, same weights, same inputs: once through the fused prologue kernel, once with the prologue
+    done by the reference's torch ops (forced by hiding the table from the module).  Outputs agree to bf16
+    rounding of the few elements that differ in the last place; cache state is compared too."""
+    torch.manual_seed(9)
+    cfg = _Cfg()
+    dev = "cuda"
+    T, D = cfg.tokens_per_frame, cfg.d_model
+    src = Attn(cfg, layer_idx=0)
+    src.rope = _TableRope(8, 16, 6, cfg.d_model // cfg.n_heads)        # 8 x 16 = 128 tokens per frame
+    with torch.no_grad():
+        src.gate_proj.weight.normal_(0, 0.5)
+        src.v_lamb.fill_(0.375)
+    src = src.to(dev).eval()
+    for name, prm in src.named_parameters():
+        prm.data = prm.data.to(torch.bfloat16)
+    fused, plain = B200Attn(src), B200Attn(src)
+    plain._fused_prologue = lambda q, pos_ids: False
+    caches = [B200StaticKVCache(cfg, batch_size=1, dtype=torch.bfloat16).to(dev) for _ in range(2)]
+    yy, xx = torch.meshgrid(torch.arange(8, device=dev), torch.arange(16, device=dev), indexing="ij")
+    v1a = v1b = None
+    for t, frozen in ((0, False), (1, False), (2, True), (2, False), (3, False)):
+        for c in caches:
+            c.set_frozen(frozen)
+        x = torch.randn(1, T, D, device=dev, dtype=torch.bfloat16)
+        pos = {"t_pos": torch.full((1, T), t, dtype=torch.long, device=dev),
+               "y_pos": yy.reshape(1, T).contiguous(), "x_pos": xx.reshape(1, T).contiguous()}
+        assert fused._fused_prologue(torch.empty(1, device=dev, dtype=torch.bfloat16), pos)
+        ya, v1a = fused(x, pos, v1a, caches[0])
+        yb, v1b = plain(x, pos, v1b, caches[1])
+        err = (ya.float() - yb.float()).abs()
+        assert err.max().item() <= 2e-2 and err.mean().item() <= 5e-4, (t, err.max().item(), err.mean().item())
+        ka, kb = caches[0].layers[0].kv.float(), caches[1].layers[0].kv.float()
+        assert (ka - kb).abs().max().item() <= 2 ** -5      # one bf16 unit in the last place at magnitude <= 4
+        assert float((ka != kb).float().mean()) <= 2e-3
+        assert torch.equal(caches[0].layers[0].written, caches[1].layers[0].written)

@@ -25,6 +25,7 @@ EXPORTS = (
     "we_b200_frame_attn",
     "we_b200_append_attend",
     "we_b200_frame_attn_static",
+    "we_b200_qkv_prologue",
     "we_b200_launch_count",
 )
 
@@ -40,6 +41,22 @@ class CacheGeom(ctypes.Structure):
 
 
 Strides3 = c_int64 * 3
+
+
+class PrologueArgs(ctypes.Structure):
+    """Mirror of `we_b200_prologue_args`."""
+    _fields_ = [
+        ("q_in", c_void_p), ("k_in", c_void_p), ("v_in", c_void_p), ("v1", c_void_p),
+        ("q_out", c_void_p), ("k_out", c_void_p), ("v_out", c_void_p),
+        ("q_in_strides", Strides3), ("k_in_strides", Strides3), ("v_in_strides", Strides3), ("v1_strides", Strides3),
+        ("q_out_strides", Strides3), ("k_out_strides", Strides3), ("v_out_strides", Strides3),
+        ("v_lamb", c_void_p), ("v_lamb_dtype", c_int32),
+        ("cos_table", c_void_p), ("sin_table", c_void_p), ("table_rows", c_int64),
+        ("t_pos", c_void_p), ("y_pos", c_void_p), ("x_pos", c_void_p), ("pos_batch_stride", c_int64),
+        ("height", c_int32), ("width", c_int32),
+        ("B", c_int32), ("T", c_int32), ("Hq", c_int32), ("Hkv", c_int32), ("Dh", c_int32),
+        ("dtype", c_int32), ("eps", c_float),
+    ]
 
 
 class WeB200Error(RuntimeError):
@@ -101,6 +118,9 @@ def load() -> ctypes.CDLL:
     lib.we_b200_frame_attn_static.argtypes = [
         c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_int32,
         c_void_p, c_void_p, c_void_p, POINTER(CacheGeom), c_float, c_void_p, c_void_p]
+
+    lib.we_b200_qkv_prologue.restype = c_int
+    lib.we_b200_qkv_prologue.argtypes = [POINTER(PrologueArgs), c_void_p, c_void_p]
 
     got = lib.we_b200_abi_version()
     if got != ABI_VERSION:

@@ -17,6 +17,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from . import ops
 from .kv_cache import B200StaticKVCache
 
 
@@ -57,6 +58,19 @@ class B200Attn(nn.Module):
                     [src.q_proj.weight, src.k_proj.weight, src.v_proj.weight], dim=0))
         self.train(src.training)
 
+    def _fused_prologue(self, q: torch.Tensor, pos_ids) -> bool:
+        """The one-pass prologue needs the table form of RoPE (`cos` / `sin` buffers indexed by
+        t*(H*W) + y*W + x, src/model/attn.py:12-31), 16-bit CUDA tensors and a head dim of 64 or 128; any
+        other RoPE module is applied through its own forward."""
+        rope = self.rope
+        if not (hasattr(rope, "cos") and hasattr(rope, "sin") and hasattr(rope, "config")):
+            return False
+        if not (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self.d_head in (64, 128)):
+            return False
+        if rope.cos.dtype != torch.float32 or rope.cos.shape[-1] != self.d_head // 2:
+            return False
+        return all(key in pos_ids for key in ("t_pos", "y_pos", "x_pos"))
+
     def forward(self, x, pos_ids, v1, kv_cache: B200StaticKVCache):
         B, T = x.shape[:2]
         q, k, v = self.qkv_proj(x).split((self.q_out, self.kv_out, self.kv_out), dim=-1)
@@ -64,12 +78,23 @@ class B200Attn(nn.Module):
         k = k.reshape(B, T, self.n_kv_heads, self.d_head).transpose(1, 2)
         v = v.reshape(B, T, self.n_kv_heads, self.d_head).transpose(1, 2)
 
-        if self.value_residual:
-            v1 = v if v1 is None else v1
-            v = torch.lerp(v, v1.view_as(v), self.v_lamb)
+        if self._fused_prologue(q, pos_ids):
+            # value residual + QK-norm + RoPE in one pass over q, k, v (src/patch_model.py:124-129)
+            residual = None
+            if self.value_residual:
+                residual = None if v1 is None else v1.view_as(v)     # lerp(v, v, w) == v: nothing to do
+                v1 = v if v1 is None else v1
+            cfg = self.rope.config
+            q, k, v = ops.qkv_prologue_op(q, k, v, residual, self.v_lamb if residual is not None else None,
+                                          self.rope.cos, self.rope.sin, pos_ids["t_pos"], pos_ids["y_pos"],
+                                          pos_ids["x_pos"], int(cfg.height), int(cfg.width))
+        else:
+            if self.value_residual:
+                v1 = v if v1 is None else v1
+                v = torch.lerp(v, v1.view_as(v), self.v_lamb)
 
-        q, k = _unit_rms(q), _unit_rms(k)
-        q, k = self.rope(q, pos_ids), self.rope(k, pos_ids)
+            q, k = _unit_rms(q), _unit_rms(k)
+            q, k = self.rope(q, pos_ids), self.rope(k, pos_ids)
 
         # cache update + attention: replaces upsert + flex_attention
         # (src/patch_model.py:131-133)

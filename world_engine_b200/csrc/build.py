@@ -11,7 +11,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
-SOURCES = ["abi.cu", "kv_append.cu", "block_mask.cu", "frame_attn.cu"]
+SOURCES = ["abi.cu", "kv_append.cu", "block_mask.cu", "frame_attn.cu", "qkv_prologue.cu"]
 HEADERS = ["common.cuh", "ptx.cuh", os.path.join("..", "..", "include", "we_b200.h")]
 
 

@@ -1,0 +1,267 @@
+// q / k / v between the projections and the cache, in one pass (sm_100a).
+//
+//   v'  = lerp(v, v1, v_lamb)                                  torch.lerp, src/model/attn.py:105-107
+//   q'  = rope(rms_norm(q)),  k' = rope(rms_norm(k))           src/model/attn.py:109-110
+//
+// One warp per (batch row, token, head) row of Dh elements: a lane holds the
+// pairs (x[2j], x[2j+1]) RoPE rotates -- j = 2 lane, 2 lane + 1 when Dh = 128
+// (one 8-byte load, two 4-byte stores), j = lane when Dh = 64.  The RMS
+// over the row is a warp shuffle reduction in fp32; the normalised row is
+// rounded to the tensor dtype before the rotation, as the reference
+// materialises it; products and sums of the rotation are rounded separately
+// (no fused multiply-add), as eager PyTorch does.  HBM-bound byte work:
+// every element is read once and written once.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace we {
+
+struct PrologueParams {
+  const uint32_t* in[3];     // q, k, v rows as packed pairs
+  const uint32_t* v1;
+  uint16_t* out[3];
+  int64_t in_s[3][3], v1_s[3], out_s[3][3];   // (b, h, t) strides in elements
+  const void* v_lamb;
+  int32_t v_lamb_dtype;
+  const float* cos_t;
+  const float* sin_t;
+  int64_t table_rows;
+  const int64_t* pos[3];     // t, y, x
+  int64_t pos_bs;
+  int32_t height, width;
+  int32_t B, T, Hq, Hkv, Dh;
+  int32_t bf16;
+  float eps;
+  int32_t* status;
+};
+
+constexpr int kPrologueThreads = 256;
+
+template <bool BF16>
+__device__ __forceinline__ float2 unpack_pair(uint32_t v) {
+  if constexpr (BF16) {
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+  } else {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ float round16(float x) {
+  if constexpr (BF16) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+  } else {
+    return __half2float(__float2half_rn(x));
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ uint16_t to16(float x) {
+  if constexpr (BF16) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(x));
+  } else {
+    return __half_as_ushort(__float2half_rn(x));
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const PrologueParams p) {
+  // Programmatic dependent launch, both ways (as in the append kernel): wait for the kernel ahead, then let the
+  // kernel behind (the attention of this layer-step) begin its on-chip set-up.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int lane = threadIdx.x & 31;
+  const int slots = p.Hq + 2 * p.Hkv;                                   // q heads, k heads, v heads
+  const int64_t rows = static_cast<int64_t>(p.B) * p.T * slots;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * (kPrologueThreads / 32) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int slot = static_cast<int>(r % slots);
+  const int64_t bt = r / slots;
+  const int t = static_cast<int>(bt % p.T);
+  const int b = static_cast<int>(bt / p.T);
+  const int which = slot < p.Hq ? 0 : (slot < p.Hq + p.Hkv ? 1 : 2);
+  const int h = which == 0 ? slot : (which == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
+  const int npair = p.Dh >> 6;                                          // pairs per lane: 1 (Dh=64) or 2 (Dh=128)
+  const uint32_t* src = p.in[which] + ((b * p.in_s[which][0] + h * p.in_s[which][1] + t * p.in_s[which][2]) >> 1);
+  uint16_t* dst = p.out[which] + b * p.out_s[which][0] + h * p.out_s[which][1] + t * p.out_s[which][2];
+  // pair index of this lane's u-th pair
+  auto pair_of = [&](int u) { return npair == 2 ? 2 * lane + u : lane; };
+  // the positions are needed for the table row: request them before anything waits
+  int64_t pt = 0, py = 0, px = 0;
+  if (which != 2) {
+    const int64_t pb = static_cast<int64_t>(b) * p.pos_bs + t;
+    pt = p.pos[0][pb];
+    py = p.pos[1][pb];
+    px = p.pos[2][pb];
+  }
+
+  float2 x[2];
+  if (npair == 2) {
+    const uint2 w = reinterpret_cast<const uint2*>(src)[lane];          // rows are 8-byte aligned when Dh = 128
+    x[0] = unpack_pair<BF16>(w.x);
+    x[1] = unpack_pair<BF16>(w.y);
+  } else {
+    x[0] = unpack_pair<BF16>(src[lane]);
+    x[1] = make_float2(0.f, 0.f);
+  }
+
+  if (which == 2) {
+    // value residual: torch.lerp's two-sided form in fp32
+    if (p.v1 != nullptr) {
+      float w;
+      if (p.v_lamb_dtype == WE_B200_F32) w = *static_cast<const float*>(p.v_lamb);
+      else if (p.v_lamb_dtype == WE_B200_BF16) w = __bfloat162float(*static_cast<const __nv_bfloat16*>(p.v_lamb));
+      else w = __half2float(*static_cast<const __half*>(p.v_lamb));
+      const uint32_t* s1 = p.v1 + ((b * p.v1_s[0] + h * p.v1_s[1] + t * p.v1_s[2]) >> 1);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (u < npair) {
+          const float2 e = unpack_pair<BF16>(s1[pair_of(u)]);
+          const float d0 = __fsub_rn(e.x, x[u].x), d1 = __fsub_rn(e.y, x[u].y);
+          if (fabsf(w) < 0.5f) {
+            x[u].x = __fadd_rn(x[u].x, __fmul_rn(w, d0));
+            x[u].y = __fadd_rn(x[u].y, __fmul_rn(w, d1));
+          } else {
+            const float om = __fsub_rn(1.0f, w);
+            x[u].x = __fsub_rn(e.x, __fmul_rn(d0, om));
+            x[u].y = __fsub_rn(e.y, __fmul_rn(d1, om));
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u < npair) {
+        const uint32_t packed = static_cast<uint32_t>(to16<BF16>(x[u].x)) | (static_cast<uint32_t>(to16<BF16>(x[u].y)) << 16);
+        reinterpret_cast<uint32_t*>(dst)[pair_of(u)] = packed;
+      }
+    }
+    return;
+  }
+
+  // weightless RMS norm in fp32 (src/model/nn.py:55-56), rounded to the tensor dtype
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) ss += x[u].x * x[u].x + x[u].y * x[u].y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rinv = 1.0f / sqrtf(ss / static_cast<float>(p.Dh) + p.eps);
+  // angles of this token (RoPE.get_angles, src/model/attn.py:22-31)
+  int64_t idx = pt * (static_cast<int64_t>(p.height) * p.width) + py * p.width + px;
+  if (idx < 0 || idx >= p.table_rows) {
+    if (lane == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_INDEX_RANGE);
+    idx = idx < 0 ? 0 : p.table_rows - 1;
+  }
+  const int half = p.Dh >> 1;
+  const float* ct = p.cos_t + idx * half;
+  const float* st = p.sin_t + idx * half;
+  float c[2], s[2];
+  if (npair == 2) {
+    const float2 c2 = reinterpret_cast<const float2*>(ct)[lane], s2 = reinterpret_cast<const float2*>(st)[lane];
+    c[0] = c2.x; c[1] = c2.y; s[0] = s2.x; s[1] = s2.y;
+  } else {
+    c[0] = ct[lane]; s[0] = st[lane]; c[1] = 0.f; s[1] = 0.f;
+  }
+  uint16_t y0[2], y1[2];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const float x0 = round16<BF16>(__fmul_rn(x[u].x, rinv)), x1 = round16<BF16>(__fmul_rn(x[u].y, rinv));
+    y0[u] = to16<BF16>(__fsub_rn(__fmul_rn(x0, c[u]), __fmul_rn(x1, s[u])));   // RoPE.forward, src/model/attn.py:37-39
+    y1[u] = to16<BF16>(__fadd_rn(__fmul_rn(x1, c[u]), __fmul_rn(x0, s[u])));
+  }
+  if (npair == 2) {
+    // first components of pairs 2 lane, 2 lane + 1 are neighbours in the first half; second components likewise
+    reinterpret_cast<uint32_t*>(dst)[lane] = static_cast<uint32_t>(y0[0]) | (static_cast<uint32_t>(y0[1]) << 16);
+    reinterpret_cast<uint32_t*>(dst + half)[lane] = static_cast<uint32_t>(y1[0]) | (static_cast<uint32_t>(y1[1]) << 16);
+  } else {
+    dst[lane] = y0[0];
+    dst[half + lane] = y1[0];
+  }
+}
+
+}  // namespace we
+
+extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* status, void* stream) {
+  using namespace we;
+  if (a == nullptr || !a->q_in || !a->k_in || !a->v_in || !a->q_out || !a->k_out || !a->v_out || !a->cos_table ||
+      !a->sin_table || !a->t_pos || !a->y_pos || !a->x_pos)
+    return WE_B200_E_NULL;
+  if (a->v1 != nullptr && a->v_lamb == nullptr) return WE_B200_E_NULL;
+  if (a->dtype != WE_B200_BF16 && a->dtype != WE_B200_F16) return WE_B200_E_DTYPE;
+  if (a->Dh != 64 && a->Dh != 128) return WE_B200_E_DTYPE;
+  if (a->v1 != nullptr && a->v_lamb_dtype != WE_B200_BF16 && a->v_lamb_dtype != WE_B200_F16 &&
+      a->v_lamb_dtype != WE_B200_F32)
+    return WE_B200_E_DTYPE;
+  if (a->B < 1 || a->T < 1 || a->Hq < 1 || a->Hkv < 1 || a->height < 1 || a->width < 1 || a->table_rows < 1 ||
+      a->pos_batch_stride < 0)
+    return WE_B200_E_SHAPE;
+  // rows are read as 8-byte (Dh = 128) or 4-byte (Dh = 64) words: strides and bases must be aligned to that
+  const int64_t* strides[7] = {a->q_in_strides, a->k_in_strides, a->v_in_strides, a->v1_strides,
+                               a->q_out_strides, a->k_out_strides, a->v_out_strides};
+  for (int i = 0; i < 7; ++i) {
+    if (i == 3 && a->v1 == nullptr) continue;
+    for (int d = 0; d < 3; ++d) {
+      if (strides[i][d] < 0) return WE_B200_E_SHAPE;
+      if (strides[i][d] & (a->Dh == 128 ? 3 : 1)) return WE_B200_E_ALIGN;
+    }
+  }
+  const void* ptrs[7] = {a->q_in, a->k_in, a->v_in, a->v1, a->q_out, a->k_out, a->v_out};
+  for (int i = 0; i < 7; ++i)
+    if (ptrs[i] != nullptr && (reinterpret_cast<uintptr_t>(ptrs[i]) & (a->Dh == 128 ? 7u : 3u))) return WE_B200_E_ALIGN;
+
+  PrologueParams p;
+  p.in[0] = static_cast<const uint32_t*>(a->q_in);
+  p.in[1] = static_cast<const uint32_t*>(a->k_in);
+  p.in[2] = static_cast<const uint32_t*>(a->v_in);
+  p.v1 = static_cast<const uint32_t*>(a->v1);
+  p.out[0] = static_cast<uint16_t*>(a->q_out);
+  p.out[1] = static_cast<uint16_t*>(a->k_out);
+  p.out[2] = static_cast<uint16_t*>(a->v_out);
+  for (int d = 0; d < 3; ++d) {
+    p.in_s[0][d] = a->q_in_strides[d];
+    p.in_s[1][d] = a->k_in_strides[d];
+    p.in_s[2][d] = a->v_in_strides[d];
+    p.v1_s[d] = a->v1 != nullptr ? a->v1_strides[d] : 0;
+    p.out_s[0][d] = a->q_out_strides[d];
+    p.out_s[1][d] = a->k_out_strides[d];
+    p.out_s[2][d] = a->v_out_strides[d];
+  }
+  p.v_lamb = a->v_lamb;
+  p.v_lamb_dtype = a->v_lamb_dtype;
+  p.cos_t = a->cos_table;
+  p.sin_t = a->sin_table;
+  p.table_rows = a->table_rows;
+  p.pos[0] = a->t_pos;
+  p.pos[1] = a->y_pos;
+  p.pos[2] = a->x_pos;
+  p.pos_bs = a->pos_batch_stride;
+  p.height = a->height;
+  p.width = a->width;
+  p.B = a->B;
+  p.T = a->T;
+  p.Hq = a->Hq;
+  p.Hkv = a->Hkv;
+  p.Dh = a->Dh;
+  p.bf16 = a->dtype == WE_B200_BF16;
+  p.eps = a->eps;
+  p.status = status;
+
+  const int64_t rows = static_cast<int64_t>(a->B) * a->T * (a->Hq + 2 * a->Hkv);
+  const int64_t blocks = (rows + kPrologueThreads / 32 - 1) / (kPrologueThreads / 32);
+  if (blocks > 0x7FFFFFFF) return WE_B200_E_LIMIT;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+  cfg.blockDim = dim3(kPrologueThreads, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = p.bf16 ? cudaLaunchKernelEx(&cfg, qkv_prologue_kernel<true>, p)
+                               : cudaLaunchKernelEx(&cfg, qkv_prologue_kernel<false>, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const cudaError_t e2 = cudaGetLastError();
+  return e2 == cudaSuccess ? WE_B200_OK : static_cast<int>(e2);
+}

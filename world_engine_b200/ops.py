@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import CacheGeom, Strides3
+from ._lib import CacheGeom, PrologueArgs, Strides3
 
 _DTYPE_CODE = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 
@@ -90,15 +90,15 @@ def status_word(device: torch.device) -> torch.Tensor:
 
 
 def check_status(device: torch.device) -> None:
-    """Synchronising health check: raises if a kernel on `device` gave up on a bounded wait."""
+    """Synchronising health check: raises if a kernel on `device` reported a device-side anomaly."""
     st = int(status_word(device).item())
     if st != 0:
         status_word(device).zero_()
-        raise RuntimeError(f"world_engine_b200: attention kernel reported device status {st} "
-                           "(a bounded wait expired; the output of that call is invalid)")
+        what = {1: "a bounded wait of the attention kernel expired; the output of that call is invalid",
+                2: "a token position points outside the RoPE table (IndexError in the reference)"}.get(st, "unknown")
+        raise RuntimeError(f"world_engine_b200: device status {st}: {what}")
 
 
-# ------------------------------------------------------------------ raw calls
 def kv_append_(kv: torch.Tensor, written: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                frame_t: torch.Tensor, tokens_per_frame: int, dilation: int, is_frozen: bool,
                mask_written: Optional[torch.Tensor] = None, frame_t_stride: int = 0) -> None:
@@ -183,6 +183,51 @@ def append_attend(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv:
     return out
 
 
+def qkv_prologue(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, v1: Optional[torch.Tensor],
+                 v_lamb: Optional[torch.Tensor], cos_table: torch.Tensor, sin_table: torch.Tensor,
+                 t_pos: torch.Tensor, y_pos: torch.Tensor, x_pos: torch.Tensor, height: int, width: int,
+                 eps: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """q, k, v `[B,H,T,Dh]` views (any strides, head dim contiguous) -> (q', k', v') as the attention and the
+    cache receive them: value residual, weightless RMS norm and RoPE in one pass (we_b200_qkv_prologue;
+    src/model/attn.py:105-110).  `v1=None` skips the residual.  Outputs are fresh `[B,T,H,Dh]`-ordered
+    buffers viewed as `[B,H,T,Dh]`, the layout the merged-QKV slices have."""
+    _require_cuda(q, k, v, v1, v_lamb, cos_table, sin_table, t_pos, y_pos, x_pos)
+    B, Hq, T, Dh = q.shape
+    Hkv = k.shape[1]
+    if cos_table.dtype != torch.float32 or sin_table.dtype != torch.float32 or not cos_table.is_contiguous() \
+            or not sin_table.is_contiguous() or cos_table.shape != sin_table.shape or cos_table.shape[-1] != Dh // 2:
+        raise ValueError("cos / sin tables must be contiguous float32 [rows, Dh/2]")
+    for name, t in (("t_pos", t_pos), ("y_pos", y_pos), ("x_pos", x_pos)):
+        if t.dtype != torch.int64 or t.shape != (B, T) or t.stride() != t_pos.stride() or t.stride(1) != 1:
+            raise ValueError(f"{name} must be int64 [B, T] with contiguous rows")
+    q_out = torch.empty((B, T, Hq, Dh), dtype=q.dtype, device=q.device).transpose(1, 2)
+    k_out = torch.empty((B, T, Hkv, Dh), dtype=k.dtype, device=k.device).transpose(1, 2)
+    v_out = torch.empty((B, T, Hkv, Dh), dtype=v.dtype, device=v.device).transpose(1, 2)
+    a = PrologueArgs()
+    a.q_in, a.k_in, a.v_in = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.v1 = v1.data_ptr() if v1 is not None else None
+    a.q_out, a.k_out, a.v_out = q_out.data_ptr(), k_out.data_ptr(), v_out.data_ptr()
+    a.q_in_strides, a.k_in_strides, a.v_in_strides = _strides3(q), _strides3(k), _strides3(v)
+    a.v1_strides = _strides3(v1) if v1 is not None else Strides3(0, 0, 0)
+    a.q_out_strides, a.k_out_strides, a.v_out_strides = _strides3(q_out), _strides3(k_out), _strides3(v_out)
+    if v1 is not None:
+        if v_lamb is None or v_lamb.numel() != 1:
+            raise ValueError("v_lamb must be a one-element tensor when v1 is given")
+        a.v_lamb, a.v_lamb_dtype = v_lamb.data_ptr(), dtype_code(v_lamb.dtype)
+    a.cos_table, a.sin_table, a.table_rows = cos_table.data_ptr(), sin_table.data_ptr(), cos_table.shape[0]
+    a.t_pos, a.y_pos, a.x_pos = t_pos.data_ptr(), y_pos.data_ptr(), x_pos.data_ptr()
+    a.pos_batch_stride = t_pos.stride(0)
+    a.height, a.width = int(height), int(width)
+    a.B, a.T, a.Hq, a.Hkv, a.Dh = B, T, Hq, Hkv, Dh
+    a.dtype = dtype_code(q.dtype)
+    a.eps = float(torch.finfo(torch.float32).eps if eps is None else eps)
+    lib = _lib.load()
+    with torch.cuda.device(q.device):
+        rc = lib.we_b200_qkv_prologue(ctypes.byref(a), status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "we_b200_qkv_prologue")
+    return q_out, k_out, v_out
+
+
 def block_mask_tables(mask_written: torch.Tensor, tokens_per_frame: int
                       ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """int32 tables of the flex BlockMask for a visibility vector (we_b200_block_mask)."""
@@ -243,3 +288,19 @@ def frame_attn_op(q: torch.Tensor, kv: torch.Tensor, written: torch.Tensor, fram
 @frame_attn_op.register_fake
 def _frame_attn_fake(q, kv, written, frame_t, tokens_per_frame, dilation, scale):
     return torch.empty_like(q)
+
+
+@torch.library.custom_op("world_engine_b200::qkv_prologue", mutates_args=())
+def qkv_prologue_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, v1: Optional[torch.Tensor],
+                    v_lamb: Optional[torch.Tensor], cos_table: torch.Tensor, sin_table: torch.Tensor,
+                    t_pos: torch.Tensor, y_pos: torch.Tensor, x_pos: torch.Tensor, height: int,
+                    width: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    return qkv_prologue(q, k, v, v1, v_lamb, cos_table, sin_table, t_pos, y_pos, x_pos, height, width)
+
+
+@qkv_prologue_op.register_fake
+def _qkv_prologue_fake(q, k, v, v1, v_lamb, cos_table, sin_table, t_pos, y_pos, x_pos, height, width):
+    def like(t):
+        B, H, T, Dh = t.shape
+        return torch.empty((B, T, H, Dh), dtype=t.dtype, device=t.device).transpose(1, 2)
+    return like(q), like(k), like(v)
