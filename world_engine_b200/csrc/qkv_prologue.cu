@@ -3,7 +3,8 @@
 //   v'  = lerp(v, v1, v_lamb)                                  torch.lerp, src/model/attn.py:105-107
 //   q'  = rope(rms_norm(q)),  k' = rope(rms_norm(k))           src/model/attn.py:109-110
 //
-// One warp per (batch row, token, head) row of Dh elements: a lane holds the
+// One warp per (batch row, token, head) row of Dh elements (the loads of a row
+// are issued together, then the table row, then arithmetic and stores); a lane holds the
 // pairs (x[2j], x[2j+1]) RoPE rotates -- j = 2 lane, 2 lane + 1 when Dh = 128
 // (one 8-byte load, two 4-byte stores), j = lane when Dh = 64.  The RMS
 // over the row is a warp shuffle reduction in fp32; the normalised row is
@@ -64,6 +65,8 @@ __device__ __forceinline__ uint16_t to16(float x) {
   }
 }
 
+constexpr int kRowsPerWarp = 1;    // rows per warp (measured at the layer shape: 1 -> 5.4 us, 2 -> 6.0 us, 4 -> 7.8 us: more warps hide more latency)
+
 template <bool BF16>
 __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const PrologueParams p) {
   // Programmatic dependent launch, both ways (as in the append kernel): wait for the kernel ahead, then let the
@@ -73,109 +76,129 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const Pr
   const int lane = threadIdx.x & 31;
   const int slots = p.Hq + 2 * p.Hkv;                                   // q heads, k heads, v heads
   const int64_t rows = static_cast<int64_t>(p.B) * p.T * slots;
-  const int64_t r = static_cast<int64_t>(blockIdx.x) * (kPrologueThreads / 32) + (threadIdx.x >> 5);
-  if (r >= rows) return;
-  const int slot = static_cast<int>(r % slots);
-  const int64_t bt = r / slots;
-  const int t = static_cast<int>(bt % p.T);
-  const int b = static_cast<int>(bt / p.T);
-  const int which = slot < p.Hq ? 0 : (slot < p.Hq + p.Hkv ? 1 : 2);
-  const int h = which == 0 ? slot : (which == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
+  const int64_t r0 = (static_cast<int64_t>(blockIdx.x) * (kPrologueThreads / 32) + (threadIdx.x >> 5)) * kRowsPerWarp;
+  if (r0 >= rows) return;
   const int npair = p.Dh >> 6;                                          // pairs per lane: 1 (Dh=64) or 2 (Dh=128)
-  const uint32_t* src = p.in[which] + ((b * p.in_s[which][0] + h * p.in_s[which][1] + t * p.in_s[which][2]) >> 1);
-  uint16_t* dst = p.out[which] + b * p.out_s[which][0] + h * p.out_s[which][1] + t * p.out_s[which][2];
+  const int half = p.Dh >> 1;
   // pair index of this lane's u-th pair
   auto pair_of = [&](int u) { return npair == 2 ? 2 * lane + u : lane; };
-  // the positions are needed for the table row: request them before anything waits
-  int64_t pt = 0, py = 0, px = 0;
-  if (which != 2) {
-    const int64_t pb = static_cast<int64_t>(b) * p.pos_bs + t;
-    pt = p.pos[0][pb];
-    py = p.pos[1][pb];
-    px = p.pos[2][pb];
-  }
+  auto load_row = [&](const uint32_t* src) {
+    uint2 w = make_uint2(0u, 0u);
+    if (npair == 2) w = reinterpret_cast<const uint2*>(src)[lane];      // rows are 8-byte aligned when Dh = 128
+    else w.x = src[lane];
+    return w;
+  };
 
-  float2 x[2];
-  if (npair == 2) {
-    const uint2 w = reinterpret_cast<const uint2*>(src)[lane];          // rows are 8-byte aligned when Dh = 128
-    x[0] = unpack_pair<BF16>(w.x);
-    x[1] = unpack_pair<BF16>(w.y);
-  } else {
-    x[0] = unpack_pair<BF16>(src[lane]);
-    x[1] = make_float2(0.f, 0.f);
-  }
-
-  if (which == 2) {
-    // value residual: torch.lerp's two-sided form in fp32
-    if (p.v1 != nullptr) {
-      float w;
-      if (p.v_lamb_dtype == WE_B200_F32) w = *static_cast<const float*>(p.v_lamb);
-      else if (p.v_lamb_dtype == WE_B200_BF16) w = __bfloat162float(*static_cast<const __nv_bfloat16*>(p.v_lamb));
-      else w = __half2float(*static_cast<const __half*>(p.v_lamb));
-      const uint32_t* s1 = p.v1 + ((b * p.v1_s[0] + h * p.v1_s[1] + t * p.v1_s[2]) >> 1);
+  // ---- phase 1: every load that depends on nothing but the row index
+  int which[kRowsPerWarp];
+  uint16_t* dst[kRowsPerWarp];
+  uint2 raw[kRowsPerWarp], raw1[kRowsPerWarp];
+  int64_t pt[kRowsPerWarp], py[kRowsPerWarp], px[kRowsPerWarp];
 #pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        if (u < npair) {
-          const float2 e = unpack_pair<BF16>(s1[pair_of(u)]);
-          const float d0 = __fsub_rn(e.x, x[u].x), d1 = __fsub_rn(e.y, x[u].y);
-          if (fabsf(w) < 0.5f) {
-            x[u].x = __fadd_rn(x[u].x, __fmul_rn(w, d0));
-            x[u].y = __fadd_rn(x[u].y, __fmul_rn(w, d1));
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    const int64_t r = r0 + i;
+    which[i] = -1;
+    if (r < rows) {
+      const int slot = static_cast<int>(r % slots);
+      const int64_t bt = r / slots;
+      const int t = static_cast<int>(bt % p.T);
+      const int b = static_cast<int>(bt / p.T);
+      const int w = slot < p.Hq ? 0 : (slot < p.Hq + p.Hkv ? 1 : 2);
+      const int h = w == 0 ? slot : (w == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
+      which[i] = w;
+      dst[i] = p.out[w] + b * p.out_s[w][0] + h * p.out_s[w][1] + t * p.out_s[w][2];
+      raw[i] = load_row(p.in[w] + ((b * p.in_s[w][0] + h * p.in_s[w][1] + t * p.in_s[w][2]) >> 1));
+      raw1[i] = make_uint2(0u, 0u);
+      pt[i] = py[i] = px[i] = 0;
+      if (w == 2) {
+        if (p.v1 != nullptr) raw1[i] = load_row(p.v1 + ((b * p.v1_s[0] + h * p.v1_s[1] + t * p.v1_s[2]) >> 1));
+      } else {
+        const int64_t pb = static_cast<int64_t>(b) * p.pos_bs + t;
+        pt[i] = p.pos[0][pb];
+        py[i] = p.pos[1][pb];
+        px[i] = p.pos[2][pb];
+      }
+    }
+  }
+  float lamb = 0.f;
+  if (p.v1 != nullptr) {
+    if (p.v_lamb_dtype == WE_B200_F32) lamb = *static_cast<const float*>(p.v_lamb);
+    else if (p.v_lamb_dtype == WE_B200_BF16) lamb = __bfloat162float(*static_cast<const __nv_bfloat16*>(p.v_lamb));
+    else lamb = __half2float(*static_cast<const __half*>(p.v_lamb));
+  }
+
+  // ---- phase 2: the angle rows (RoPE.get_angles, src/model/attn.py:22-31), which need the positions
+  float2 cs[kRowsPerWarp], sn[kRowsPerWarp];
+#pragma unroll
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    cs[i] = sn[i] = make_float2(0.f, 0.f);
+    if (which[i] == 0 || which[i] == 1) {
+      int64_t idx = pt[i] * (static_cast<int64_t>(p.height) * p.width) + py[i] * p.width + px[i];
+      if (idx < 0 || idx >= p.table_rows) {
+        if (lane == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_INDEX_RANGE);
+        idx = idx < 0 ? 0 : p.table_rows - 1;
+      }
+      const float* ct = p.cos_t + idx * half;
+      const float* st = p.sin_t + idx * half;
+      if (npair == 2) {
+        cs[i] = reinterpret_cast<const float2*>(ct)[lane];
+        sn[i] = reinterpret_cast<const float2*>(st)[lane];
+      } else {
+        cs[i].x = ct[lane];
+        sn[i].x = st[lane];
+      }
+    }
+  }
+
+  // ---- phase 3: arithmetic and stores
+#pragma unroll
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    if (which[i] < 0) continue;                                          // (uniform over the warp)
+    float2 x[2] = {unpack_pair<BF16>(raw[i].x), unpack_pair<BF16>(raw[i].y)};
+    if (which[i] == 2) {
+      // value residual: torch.lerp's two-sided form in fp32 (src/model/attn.py:105-107)
+      if (p.v1 != nullptr) {
+        const float2 e[2] = {unpack_pair<BF16>(raw1[i].x), unpack_pair<BF16>(raw1[i].y)};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const float d0 = __fsub_rn(e[u].x, x[u].x), d1 = __fsub_rn(e[u].y, x[u].y);
+          if (fabsf(lamb) < 0.5f) {
+            x[u].x = __fadd_rn(x[u].x, __fmul_rn(lamb, d0));
+            x[u].y = __fadd_rn(x[u].y, __fmul_rn(lamb, d1));
           } else {
-            const float om = __fsub_rn(1.0f, w);
-            x[u].x = __fsub_rn(e.x, __fmul_rn(d0, om));
-            x[u].y = __fsub_rn(e.y, __fmul_rn(d1, om));
+            const float om = __fsub_rn(1.0f, lamb);
+            x[u].x = __fsub_rn(e[u].x, __fmul_rn(d0, om));
+            x[u].y = __fsub_rn(e[u].y, __fmul_rn(d1, om));
           }
         }
       }
+      const uint32_t a0 = static_cast<uint32_t>(to16<BF16>(x[0].x)) | (static_cast<uint32_t>(to16<BF16>(x[0].y)) << 16);
+      const uint32_t a1 = static_cast<uint32_t>(to16<BF16>(x[1].x)) | (static_cast<uint32_t>(to16<BF16>(x[1].y)) << 16);
+      if (npair == 2) reinterpret_cast<uint2*>(dst[i])[lane] = make_uint2(a0, a1);
+      else reinterpret_cast<uint32_t*>(dst[i])[lane] = a0;
+      continue;
     }
+    // weightless RMS norm in fp32 (src/model/nn.py:55-56), rounded to the tensor dtype
+    float ss = x[0].x * x[0].x + x[0].y * x[0].y + x[1].x * x[1].x + x[1].y * x[1].y;   // (second pair is 0 at Dh=64)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rinv = 1.0f / sqrtf(ss / static_cast<float>(p.Dh) + p.eps);
+    const float c[2] = {cs[i].x, cs[i].y}, s[2] = {sn[i].x, sn[i].y};
+    uint16_t y0[2], y1[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      if (u < npair) {
-        const uint32_t packed = static_cast<uint32_t>(to16<BF16>(x[u].x)) | (static_cast<uint32_t>(to16<BF16>(x[u].y)) << 16);
-        reinterpret_cast<uint32_t*>(dst)[pair_of(u)] = packed;
-      }
+      const float x0 = round16<BF16>(__fmul_rn(x[u].x, rinv)), x1 = round16<BF16>(__fmul_rn(x[u].y, rinv));
+      y0[u] = to16<BF16>(__fsub_rn(__fmul_rn(x0, c[u]), __fmul_rn(x1, s[u])));   // RoPE.forward, src/model/attn.py:37-39
+      y1[u] = to16<BF16>(__fadd_rn(__fmul_rn(x1, c[u]), __fmul_rn(x0, s[u])));
     }
-    return;
-  }
-
-  // weightless RMS norm in fp32 (src/model/nn.py:55-56), rounded to the tensor dtype
-  float ss = 0.f;
-#pragma unroll
-  for (int u = 0; u < 2; ++u) ss += x[u].x * x[u].x + x[u].y * x[u].y;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-  const float rinv = 1.0f / sqrtf(ss / static_cast<float>(p.Dh) + p.eps);
-  // angles of this token (RoPE.get_angles, src/model/attn.py:22-31)
-  int64_t idx = pt * (static_cast<int64_t>(p.height) * p.width) + py * p.width + px;
-  if (idx < 0 || idx >= p.table_rows) {
-    if (lane == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_INDEX_RANGE);
-    idx = idx < 0 ? 0 : p.table_rows - 1;
-  }
-  const int half = p.Dh >> 1;
-  const float* ct = p.cos_t + idx * half;
-  const float* st = p.sin_t + idx * half;
-  float c[2], s[2];
-  if (npair == 2) {
-    const float2 c2 = reinterpret_cast<const float2*>(ct)[lane], s2 = reinterpret_cast<const float2*>(st)[lane];
-    c[0] = c2.x; c[1] = c2.y; s[0] = s2.x; s[1] = s2.y;
-  } else {
-    c[0] = ct[lane]; s[0] = st[lane]; c[1] = 0.f; s[1] = 0.f;
-  }
-  uint16_t y0[2], y1[2];
-#pragma unroll
-  for (int u = 0; u < 2; ++u) {
-    const float x0 = round16<BF16>(__fmul_rn(x[u].x, rinv)), x1 = round16<BF16>(__fmul_rn(x[u].y, rinv));
-    y0[u] = to16<BF16>(__fsub_rn(__fmul_rn(x0, c[u]), __fmul_rn(x1, s[u])));   // RoPE.forward, src/model/attn.py:37-39
-    y1[u] = to16<BF16>(__fadd_rn(__fmul_rn(x1, c[u]), __fmul_rn(x0, s[u])));
-  }
-  if (npair == 2) {
-    // first components of pairs 2 lane, 2 lane + 1 are neighbours in the first half; second components likewise
-    reinterpret_cast<uint32_t*>(dst)[lane] = static_cast<uint32_t>(y0[0]) | (static_cast<uint32_t>(y0[1]) << 16);
-    reinterpret_cast<uint32_t*>(dst + half)[lane] = static_cast<uint32_t>(y1[0]) | (static_cast<uint32_t>(y1[1]) << 16);
-  } else {
-    dst[lane] = y0[0];
-    dst[half + lane] = y1[0];
+    if (npair == 2) {
+      // first components of pairs 2 lane, 2 lane + 1 are neighbours in the first half; second components likewise
+      reinterpret_cast<uint32_t*>(dst[i])[lane] = static_cast<uint32_t>(y0[0]) | (static_cast<uint32_t>(y0[1]) << 16);
+      reinterpret_cast<uint32_t*>(dst[i] + half)[lane] = static_cast<uint32_t>(y1[0]) | (static_cast<uint32_t>(y1[1]) << 16);
+    } else {
+      dst[i][pair_of(0)] = y0[0];
+      dst[i][half + pair_of(0)] = y1[0];
+    }
   }
 }
 
@@ -247,7 +270,8 @@ extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* sta
   p.status = status;
 
   const int64_t rows = static_cast<int64_t>(a->B) * a->T * (a->Hq + 2 * a->Hkv);
-  const int64_t blocks = (rows + kPrologueThreads / 32 - 1) / (kPrologueThreads / 32);
+  const int64_t per_block = (kPrologueThreads / 32) * kRowsPerWarp;
+  const int64_t blocks = (rows + per_block - 1) / per_block;
   if (blocks > 0x7FFFFFFF) return WE_B200_E_LIMIT;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
