@@ -75,8 +75,9 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const Pr
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int slots = p.Hq + 2 * p.Hkv;                                   // q heads, k heads, v heads
-  const int64_t rows = static_cast<int64_t>(p.B) * p.T * slots;
-  const int64_t r0 = (static_cast<int64_t>(blockIdx.x) * (kPrologueThreads / 32) + (threadIdx.x >> 5)) * kRowsPerWarp;
+  // (row indices fit 32 bits: the host rejects larger problems; 64-bit divisions would dominate the kernel)
+  const uint32_t rows = static_cast<uint32_t>(p.B) * static_cast<uint32_t>(p.T) * static_cast<uint32_t>(slots);
+  const uint32_t r0 = (blockIdx.x * (kPrologueThreads / 32) + (threadIdx.x >> 5)) * kRowsPerWarp;
   if (r0 >= rows) return;
   const int npair = p.Dh >> 6;                                          // pairs per lane: 1 (Dh=64) or 2 (Dh=128)
   const int half = p.Dh >> 1;
@@ -96,13 +97,13 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const Pr
   int64_t pt[kRowsPerWarp], py[kRowsPerWarp], px[kRowsPerWarp];
 #pragma unroll
   for (int i = 0; i < kRowsPerWarp; ++i) {
-    const int64_t r = r0 + i;
+    const uint32_t r = r0 + i;
     which[i] = -1;
     if (r < rows) {
-      const int slot = static_cast<int>(r % slots);
-      const int64_t bt = r / slots;
-      const int t = static_cast<int>(bt % p.T);
-      const int b = static_cast<int>(bt / p.T);
+      const uint32_t bt = r / static_cast<uint32_t>(slots);
+      const int slot = static_cast<int>(r - bt * slots);
+      const int b = static_cast<int>(bt / static_cast<uint32_t>(p.T));
+      const int t = static_cast<int>(bt - b * p.T);
       const int w = slot < p.Hq ? 0 : (slot < p.Hq + p.Hkv ? 1 : 2);
       const int h = w == 0 ? slot : (w == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
       which[i] = w;
@@ -272,7 +273,7 @@ extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* sta
   const int64_t rows = static_cast<int64_t>(a->B) * a->T * (a->Hq + 2 * a->Hkv);
   const int64_t per_block = (kPrologueThreads / 32) * kRowsPerWarp;
   const int64_t blocks = (rows + per_block - 1) / per_block;
-  if (blocks > 0x7FFFFFFF) return WE_B200_E_LIMIT;
+  if (blocks > 0x7FFFFFFF || rows > 0x7FFFFFFF) return WE_B200_E_LIMIT;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
   cfg.blockDim = dim3(kPrologueThreads, 1, 1);
