@@ -200,6 +200,27 @@ WE_B200_API int we_b200_frame_attn_static(const void* q, const int64_t* q_stride
                               int32_t* status, void* stream);
 
 /*
+ * we_b200_append_attend with the head gate applied to the output rows on their
+ * way out (next to the hot path: src/model/attn.py:116-119, src/patch_model.py:133-137):
+ *   out[b,h,t,:] = attention(...)[b,h,t,:] * g[b,h,t]
+ * `gate` is a [B,Hq,T] view (strides (b,h,t) in elements) of the dtype of q;
+ * with gate_is_logits != 0 the factor is sigmoid(gate) rounded to that dtype
+ * (the reference's `gates = torch.sigmoid(gate_proj(x[..., :H]))`), otherwise
+ * the values are used as they are.  The product is rounded once, from the fp32
+ * accumulator (the reference rounds the attention output first).
+ */
+WE_B200_API int we_b200_append_attend_gated(const void* q, const int64_t* q_strides_host,
+                                            void* out, const int64_t* out_strides_host, int32_t Hq,
+                                            const void* k_new, const int64_t* k_strides_host,
+                                            const void* v_new, const int64_t* v_strides_host,
+                                            void* kv, uint8_t* written, uint8_t* mask_written,
+                                            const int64_t* frame_t, const we_b200_cache_geom* geom_host,
+                                            int is_frozen, float scale,
+                                            const void* gate, const int64_t* gate_strides_host, int gate_is_logits,
+                                            void* workspace, size_t workspace_bytes,
+                                            int32_t* status, void* stream);
+
+/*
  * What happens to q, k, v between the projections and the cache, in one pass
  * (next to the hot path: src/model/attn.py:105-110, src/patch_model.py:124-129):
  *   v'  = lerp(v, v1, v_lamb)                 if v1 != NULL     (torch.lerp, :105-107)

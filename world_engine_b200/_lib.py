@@ -24,6 +24,7 @@ EXPORTS = (
     "we_b200_attn_workspace_bytes",
     "we_b200_frame_attn",
     "we_b200_append_attend",
+    "we_b200_append_attend_gated",
     "we_b200_frame_attn_static",
     "we_b200_qkv_prologue",
     "we_b200_launch_count",
@@ -112,6 +113,14 @@ def load() -> ctypes.CDLL:
         c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_int32,
         c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64),
         c_void_p, c_void_p, c_void_p, c_void_p, POINTER(CacheGeom), c_int, c_float,
+        c_void_p, c_size_t, c_void_p, c_void_p]
+
+    lib.we_b200_append_attend_gated.restype = c_int
+    lib.we_b200_append_attend_gated.argtypes = [
+        c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64), c_int32,
+        c_void_p, POINTER(c_int64), c_void_p, POINTER(c_int64),
+        c_void_p, c_void_p, c_void_p, c_void_p, POINTER(CacheGeom), c_int, c_float,
+        c_void_p, POINTER(c_int64), c_int,
         c_void_p, c_size_t, c_void_p, c_void_p]
 
     lib.we_b200_frame_attn_static.restype = c_int

@@ -98,11 +98,17 @@ class B200Attn(nn.Module):
 
         # cache update + attention: replaces upsert + flex_attention
         # (src/patch_model.py:131-133)
-        y = kv_cache.append_and_attend(q, k, v, pos_ids, self.layer_idx)
-
-        if self.gated_attn:
-            gates = torch.sigmoid(self.gate_proj(x[..., : self.n_heads]))
-            y = y * gates.permute(0, 2, 1).unsqueeze(-1)
+        # with the head gate (src/patch_model.py:135-137) applied to the rows on their way out of the kernel:
+        # sigmoid(gate_proj(x[..., :H])) as a [B, H, T] view of the [B, T, H] logits
+        if self.gated_attn and q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
+            logits = self.gate_proj(x[..., : self.n_heads])
+            y = kv_cache.append_and_attend(q, k, v, pos_ids, self.layer_idx, gate=logits.permute(0, 2, 1),
+                                           gate_is_logits=True)
+        else:
+            y = kv_cache.append_and_attend(q, k, v, pos_ids, self.layer_idx)
+            if self.gated_attn:
+                gates = torch.sigmoid(self.gate_proj(x[..., : self.n_heads]))
+                y = y * gates.permute(0, 2, 1).unsqueeze(-1)
 
         y = y.transpose(1, 2).reshape(B, T, -1)
         return self.out_proj(y), v1

@@ -79,9 +79,16 @@ struct FusedAppend {
   int is_frozen;
 };
 
+// A per-(batch row, head, token) factor applied to the output rows on their way out.
+struct OutputGate {
+  const void* gate;       // [B,H,T] view, same 16-bit dtype as q
+  const int64_t* gs;      // strides (b, h, t) in elements
+  int is_logits;          // 1: the factor is sigmoid(value), rounded to the dtype like the reference's tensor
+};
+
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
                       const uint8_t* written, const int64_t* frame_t, const we_b200_cache_geom* g, float scale,
                       void* workspace, size_t workspace_bytes, int32_t* status, bool after_append,
-                      const FusedAppend* fused_append, cudaStream_t stream);
+                      const FusedAppend* fused_append, cudaStream_t stream, const OutputGate* gate = nullptr);
 
 }  // namespace we

@@ -126,6 +126,10 @@ struct AttnParams {
   int32_t is_frozen;
   int32_t kn_perm[3], vn_perm[3];
   uint8_t* written_w;
+  // optional per-row output factor (the head gate of src/model/attn.py:117-119)
+  const uint16_t* gate;
+  int64_t gate_s[3];             // strides (b, h, t) in elements
+  int32_t gate_logits;           // 1: apply sigmoid and round to the dtype first
 };
 
 #ifdef WE_ATTN_DEBUG
@@ -362,6 +366,18 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int kvh = h / (p.Hq / p.Hkv);
   const int q0 = qt * kBlockM;
   const uint8_t* wr = p.written + static_cast<int64_t>(b) * p.written_batch_stride;
+  // Factor of output row `r` of this tile: 1, or the head gate (sigmoid of the logit, rounded to the tensors'
+  // dtype as the reference's `gates` tensor is, src/model/attn.py:117-119).
+  auto row_gate = [&](int r) -> float {
+    if (p.gate == nullptr || q0 + r >= p.T) return 1.f;
+    const uint16_t raw = p.gate[b * p.gate_s[0] + h * p.gate_s[1] + static_cast<int64_t>(q0 + r) * p.gate_s[2]];
+    float gv = BF16 ? __uint_as_float(static_cast<uint32_t>(raw) << 16) : __half2float(__ushort_as_half(raw));
+    if (p.gate_logits) {
+      gv = 1.0f / (1.0f + expf(-gv));
+      gv = BF16 ? __bfloat162float(__float2bfloat16_rn(gv)) : __half2float(__float2half_rn(gv));
+    }
+    return gv;
+  };
 #ifdef WE_ATTN_DEBUG
   const int dbg_mode = g_mode;   // read once: a global load inside the single-thread issue loop stalls the tensor pipe
   const long long t_start = trace_clock();
@@ -876,7 +892,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (p.cluster_merge) {
       float wgt = 1.0f;
       if (p.nsplit == 1) {
-        wgt = 1.0f / l_cta;
+        wgt = (1.0f / l_cta) * row_gate(row);
       } else {
         cluster_wait_acquire();       // every CTA of the cluster has initialised its barriers (long ago)
         // every CTA of the cluster learns every split's (m, l): group 0 sends its rows' pair to all peers as
@@ -1016,7 +1032,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int e = 0; e < kHalf; ++e) acc[e] = fmaf(w2, __ldcg(os2 + e * kBlockM), acc[e]);
         }
-        const float inv = 1.0f / den;
+        const float inv = (1.0f / den) * row_gate(row);
         if (in_range) {
 #pragma unroll
           for (int e = 0; e < kHalf / 8; ++e) {
@@ -1105,7 +1121,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         w_u[u] = l_u[u] > 0.f ? fast_exp2(w_u[u] - m_all) : 0.f;
         den = fmaf(l_u[u], w_u[u], den);
       }
-      const float inv = den > 0.f ? __fdividef(1.0f, den) : 0.f;
+      const float inv = (den > 0.f ? __fdividef(1.0f, den) : 0.f) * row_gate(row);
 #pragma unroll
       for (int u = 0; u < NS; ++u) w_u[u] *= inv;
       if (tid == 0) WE_TRACE(239);
@@ -1373,7 +1389,7 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
 int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t* os, int Hq, const void* kv,
                       const uint8_t* written, const int64_t* frame_t, const we_b200_cache_geom* g, float scale,
                       void* workspace, size_t workspace_bytes, int32_t* status, bool after_append,
-                      const FusedAppend* fa, cudaStream_t stream) {
+                      const FusedAppend* fa, cudaStream_t stream, const OutputGate* og) {
   if (!q || !out || !kv || !written || !frame_t) return WE_B200_E_NULL;
   int rc = check_geom(g);
   if (rc != WE_B200_OK) return rc;
@@ -1436,6 +1452,19 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   p.fused = 0;
   p.is_frozen = 0;
   p.written_w = nullptr;
+  p.gate = nullptr;
+  p.gate_logits = 0;
+  for (int i = 0; i < 3; ++i) p.gate_s[i] = 0;
+  if (og != nullptr && og->gate != nullptr) {
+    if (og->gs == nullptr) return WE_B200_E_NULL;
+    for (int i = 0; i < 3; ++i) {
+      if (og->gs[i] < 0) return WE_B200_E_SHAPE;
+      p.gate_s[i] = og->gs[i];
+    }
+    if (reinterpret_cast<uintptr_t>(og->gate) & 1u) return WE_B200_E_ALIGN;
+    p.gate = static_cast<const uint16_t*>(og->gate);
+    p.gate_logits = og->is_logits ? 1 : 0;
+  }
   for (int i = 0; i < 3; ++i) p.kn_perm[i] = p.vn_perm[i] = i;
   if (fa != nullptr) {
     // the append rides along: new rows are read through their own tensor maps and written back through the

@@ -106,12 +106,19 @@ class B200LayerKVCache(nn.Module):
 
     # -- fused layer-step ---------------------------------------------------
     def append_and_attend(self, q: Tensor, k: Tensor, v: Tensor, pos_ids: Mapping[str, Tensor],
-                          is_frozen: bool, scale: float = 0.0) -> Tensor:
+                          is_frozen: bool, scale: float = 0.0, gate: Optional[Tensor] = None,
+                          gate_is_logits: bool = False) -> Tensor:
         """Append the frame and attend to the cache: what upsert + flex_attention
         do at src/model/attn.py:113-116, without a BlockMask (one launch when the
-        tail frame is made of whole 128-key tiles, else append + attention)."""
+        tail frame is made of whole 128-key tiles, else append + attention).
+        `gate` ([B,Hq,T], q's dtype) multiplies the output rows, after a sigmoid
+        when `gate_is_logits` (the head gate of src/model/attn.py:117-119)."""
         t_pos = self._frame_t(pos_ids)
         self._check(k, t_pos)
+        if gate is not None:
+            return ops.append_attend_gated_op(q, k, v, self.kv, self.written.view(torch.uint8), t_pos, gate,
+                                              self.tpf, self.pinned_dilation, bool(is_frozen), float(scale),
+                                              bool(gate_is_logits))
         return ops.append_attend_op(q, k, v, self.kv, self.written.view(torch.uint8), t_pos,
                                     self.tpf, self.pinned_dilation, bool(is_frozen), float(scale))
 
@@ -155,5 +162,6 @@ class B200StaticKVCache(nn.Module):
         return self.layers[layer].upsert_kv(k, v, pos_ids, self._is_frozen)
 
     def append_and_attend(self, q: Tensor, k: Tensor, v: Tensor, pos_ids: Mapping[str, Tensor],
-                          layer: int, scale: float = 0.0) -> Tensor:
-        return self.layers[layer].append_and_attend(q, k, v, pos_ids, self._is_frozen, scale)
+                          layer: int, scale: float = 0.0, gate: Optional[Tensor] = None,
+                          gate_is_logits: bool = False) -> Tensor:
+        return self.layers[layer].append_and_attend(q, k, v, pos_ids, self._is_frozen, scale, gate, gate_is_logits)

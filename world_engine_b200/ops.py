@@ -161,24 +161,33 @@ def frame_attn_no_alloc(q: torch.Tensor, out: torch.Tensor, status: torch.Tensor
 def append_attend(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv: torch.Tensor,
                   written: torch.Tensor, frame_t: torch.Tensor, tokens_per_frame: int, dilation: int,
                   is_frozen: bool, scale: float = 0.0, out: Optional[torch.Tensor] = None,
-                  mask_written: Optional[torch.Tensor] = None, frame_t_stride: int = 0) -> torch.Tensor:
-    """One layer-step: append the frame, then attend (we_b200_append_attend)."""
-    _require_cuda(q, k_new, v_new, kv, written, frame_t, mask_written)
+                  mask_written: Optional[torch.Tensor] = None, frame_t_stride: int = 0,
+                  gate: Optional[torch.Tensor] = None, gate_is_logits: bool = False) -> torch.Tensor:
+    """One layer-step: append the frame, then attend (we_b200_append_attend).  With `gate` (a `[B,Hq,T]` view of
+    q's dtype) the output rows are multiplied by it, or by its sigmoid when `gate_is_logits`, on their way out
+    (we_b200_append_attend_gated; src/model/attn.py:117-119)."""
+    _require_cuda(q, k_new, v_new, kv, written, frame_t, mask_written, gate)
     g = make_geom(kv, written, tokens_per_frame, dilation, frame_t_stride)
     if out is None:
         out = torch.empty_like(q)
     lib = _lib.load()
     B, Hq, T, Dh = q.shape
+    if gate is not None and (gate.shape != (B, Hq, T) or gate.dtype != q.dtype):
+        raise ValueError("gate must be a [B, Hq, T] view of q's dtype")
     with torch.cuda.device(q.device):
         need = lib.we_b200_attn_workspace_bytes(B, Hq, T, Dh, g.L)
         ws = workspace_for(q.device, need)
-        rc = lib.we_b200_append_attend(
-            q.data_ptr(), _strides3(q), out.data_ptr(), _strides3(out), Hq,
-            k_new.data_ptr(), _strides3(k_new), v_new.data_ptr(), _strides3(v_new),
-            kv.data_ptr(), written.data_ptr(),
-            mask_written.data_ptr() if mask_written is not None else None,
-            frame_t.data_ptr(), ctypes.byref(g), int(bool(is_frozen)), float(scale),
-            ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        head = (q.data_ptr(), _strides3(q), out.data_ptr(), _strides3(out), Hq,
+                k_new.data_ptr(), _strides3(k_new), v_new.data_ptr(), _strides3(v_new),
+                kv.data_ptr(), written.data_ptr(),
+                mask_written.data_ptr() if mask_written is not None else None,
+                frame_t.data_ptr(), ctypes.byref(g), int(bool(is_frozen)), float(scale))
+        tail = (ws.data_ptr(), ws.numel(), status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        if gate is None:
+            rc = lib.we_b200_append_attend(*head, *tail)
+        else:
+            rc = lib.we_b200_append_attend_gated(*head, gate.data_ptr(), Strides3(*gate.stride()),
+                                                 int(bool(gate_is_logits)), *tail)
     _lib.check(rc, "we_b200_append_attend")
     return out
 
@@ -304,3 +313,18 @@ def _qkv_prologue_fake(q, k, v, v1, v_lamb, cos_table, sin_table, t_pos, y_pos, 
         B, H, T, Dh = t.shape
         return torch.empty((B, T, H, Dh), dtype=t.dtype, device=t.device).transpose(1, 2)
     return like(q), like(k), like(v)
+
+
+@torch.library.custom_op("world_engine_b200::append_attend_gated", mutates_args=("kv", "written"))
+def append_attend_gated_op(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, kv: torch.Tensor,
+                           written: torch.Tensor, frame_t: torch.Tensor, gate: torch.Tensor,
+                           tokens_per_frame: int, dilation: int, is_frozen: bool, scale: float,
+                           gate_is_logits: bool) -> torch.Tensor:
+    return append_attend(q, k_new, v_new, kv, written, frame_t, tokens_per_frame, dilation, is_frozen, scale,
+                         gate=gate, gate_is_logits=gate_is_logits)
+
+
+@append_attend_gated_op.register_fake
+def _append_attend_gated_fake(q, k_new, v_new, kv, written, frame_t, gate, tokens_per_frame, dilation, is_frozen,
+                              scale, gate_is_logits):
+    return torch.empty_like(q)
