@@ -195,3 +195,46 @@ def test_module_with_table_rope_uses_the_one_pass_prologue_and_agrees_with_the_t
         assert (ka - kb).abs().max().item() <= 2 ** -5      # one bf16 unit in the last place at magnitude <= 4
         assert float((ka != kb).float().mean()) <= 2e-3
         assert torch.equal(caches[0].layers[0].written, caches[1].layers[0].written)
+
+
+@pytest.mark.gpu
+def test_module_traces_as_one_graph_with_the_custom_ops():
+    """The reference runs its model under torch.compile(fullgraph=True) (src/world_engine.py:139,148).  The
+    module must trace into ONE graph: custom ops with fake implementations and declared mutations, no host
+    synchronisation, the frame counter read on the device.  Checked with the ahead-of-time tracing backend
+    (no code generation): same outputs and same cache state as the eager module."""
+    torch.manual_seed(13)
+    cfg = _Cfg()
+    dev = "cuda"
+    T, D = cfg.tokens_per_frame, cfg.d_model
+    src = Attn(cfg, layer_idx=0)
+    src.rope = _TableRope(8, 16, 6, cfg.d_model // cfg.n_heads)
+    with torch.no_grad():
+        src.gate_proj.weight.normal_(0, 0.5)
+    src = src.to(dev).eval()
+    for prm in src.parameters():
+        prm.data = prm.data.to(torch.bfloat16)
+    eager = B200Attn(src)
+    caches = [B200StaticKVCache(cfg, batch_size=1, dtype=torch.bfloat16).to(dev) for _ in range(2)]
+    for c in caches:
+        for layer in c.layers:
+            layer.validate = False          # the eager-only argument checks read values on the host
+    yy, xx = torch.meshgrid(torch.arange(8, device=dev), torch.arange(16, device=dev), indexing="ij")
+
+    def step(mod, cache, x, pos, v1):
+        return mod(x, pos, v1, cache)
+
+    compiled = torch.compile(step, fullgraph=True, backend="aot_eager")
+    v1a = v1b = None
+    for t, frozen in ((0, False), (1, True), (1, False), (2, False)):
+        for c in caches:
+            c.set_frozen(frozen)
+        x = torch.randn(1, T, D, device=dev, dtype=torch.bfloat16)
+        pos = {"t_pos": torch.full((1, T), t, dtype=torch.long, device=dev),
+               "y_pos": yy.reshape(1, T).contiguous(), "x_pos": xx.reshape(1, T).contiguous()}
+        with torch.no_grad():
+            ya, v1a = step(eager, caches[0], x, pos, v1a)
+            yb, v1b = compiled(eager, caches[1], x, pos, v1b)
+        assert torch.equal(ya, yb), f"frame {t}: traced output differs from eager"
+        assert torch.equal(caches[0].layers[0].kv.view(torch.int16), caches[1].layers[0].kv.view(torch.int16))
+        assert torch.equal(caches[0].layers[0].written, caches[1].layers[0].written)
