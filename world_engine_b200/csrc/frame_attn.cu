@@ -749,6 +749,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const bool hide = s_slot[1] != 0;
     float m_run = -INFINITY;  // running row maximum, log2 domain, possibly stale by <= threshold
     float l_run = 0.f;        // row sum over this group's keys
+    // Second half of the split-phase cluster barrier (every CTA of the cluster has initialised its mbarriers),
+    // needed before the first access to a peer's shared memory after the loop; by now it completes at once.
+    if (p.cluster_merge && p.nsplit > 1) cluster_wait_acquire();
     for (int i = 0; i < n; ++i) {
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
@@ -870,13 +873,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_wait(o_final, 0, s_abort);   // (the per-tile barriers of the other group were never followed here)
       tc_fence_after();
     }
-    // the producer warps are done with the rings (tensor stores of new-frame tiles have read them)
-    named_bar_sync(5, kSoftmaxThreads + 64);
     if (row == 0) WE_TRACE(224 + wg);
-    // merge the two groups' streams: exchange (m, l); each group then combines one half of the head dim
+    // merge the two groups' streams: exchange (m, l); each group then combines one half of the head dim.  The
+    // barrier of the exchange is also the one the producer warps arrive on when they are done with the rings
+    // (tensor stores of new-frame tiles have read them).
     s_x[(wg * 2 + 0) * kBlockM + row] = m_run;
     s_x[(wg * 2 + 1) * kBlockM + row] = l_run;
-    named_bar_sync(1, kSoftmaxThreads);
+    named_bar_sync(5, kSoftmaxThreads + 64);
     const float m_oth = s_x[((wg ^ 1) * 2 + 0) * kBlockM + row];
     const float l_oth = s_x[((wg ^ 1) * 2 + 1) * kBlockM + row];
     const float m_cta = fmaxf(m_run, m_oth);                       // -inf when the split got no tile
@@ -894,7 +897,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (p.nsplit == 1) {
         wgt = (1.0f / l_cta) * row_gate(row);
       } else {
-        cluster_wait_acquire();       // every CTA of the cluster has initialised its barriers (long ago)
         // every CTA of the cluster learns every split's (m, l): group 0 sends its rows' pair to all peers as
         // asynchronous stores that complete on the peer's barrier (no fence, no extra arrival).  The pairs
         // are consumed only when the rows are summed, so their flight overlaps the staging below.
