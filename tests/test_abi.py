@@ -99,3 +99,36 @@ def test_ops_refuse_cpu_tensors():
     pos = {"t_pos": torch.zeros(1, 64, dtype=torch.long)}
     with pytest.raises(RuntimeError, match="no CPU path"):
         cache.append_and_attend(x, x, x, pos, True)
+
+
+def test_prologue_and_gate_reject_bad_arguments(lib):
+    from world_engine_b200._lib import PrologueArgs
+    def args(**kw):
+        a = PrologueArgs()
+        for name in ("q_in", "k_in", "v_in", "q_out", "k_out", "v_out", "cos_table", "sin_table", "t_pos", "y_pos",
+                     "x_pos"):
+            setattr(a, name, FAKE)
+        s = Strides3(256 * 48 * 128, 128, 48 * 128)
+        for name in ("q_in_strides", "k_in_strides", "v_in_strides", "q_out_strides", "k_out_strides",
+                     "v_out_strides"):
+            setattr(a, name, s)
+        a.table_rows, a.pos_batch_stride, a.height, a.width = 1024, 256, 16, 16
+        a.B, a.T, a.Hq, a.Hkv, a.Dh, a.dtype, a.eps = 1, 256, 16, 16, 128, _lib.BF16, 1e-6
+        for k, v in kw.items():
+            setattr(a, k, v)
+        return a
+    call = lambda a: lib.we_b200_qkv_prologue(ctypes.byref(a), None, None)
+    assert lib.we_b200_qkv_prologue(None, None, None) == -1
+    assert call(args(q_in=None)) == -1
+    assert call(args(v1=FAKE)) == -1                                 # a residual source needs its weight
+    assert call(args(dtype=_lib.F32)) == -4                          # 16-bit tensors only
+    assert call(args(Dh=96)) == -4
+    assert call(args(T=0)) == -3
+    assert call(args(q_in=FAKE + 4)) == -2                           # rows of Dh=128 are read as 8-byte words
+    assert call(args(k_in_strides=Strides3(256 * 48 * 128, 128, 48 * 128 + 2))) == -2
+    # the gated layer-step needs its gate
+    s = Strides3(4 * 64 * 64, 64 * 64, 64)
+    g = _geom()
+    rc = lib.we_b200_append_attend_gated(FAKE, s, FAKE, s, 4, FAKE, s, FAKE, s, FAKE, FAKE, None, FAKE,
+                                         ctypes.byref(g), 1, 0.0, None, None, 1, FAKE, 1 << 30, None, None)
+    assert rc == -1
