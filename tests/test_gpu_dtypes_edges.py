@@ -73,3 +73,32 @@ def test_first_frames_of_a_session_at_layer_size():
             assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"frame {t} frozen={frozen}: {mx} {mean}"
             assert torch.isfinite(out.float()).all()
     ops.check_status(torch.device("cuda"))
+
+
+def test_long_ring_near_the_tile_capacity():
+    """65536-token ring (512 frames of 128 tokens) + tail = 513 key tiles for one head: the split over a cluster
+    of 8 CTAs with 64 tiles each, half of the documented capacity of 1024 tiles per (row, head).  The ring is
+    filled directly (replaying 512 frames would only exercise the append), then two steps are checked."""
+    from tests import gpu_helpers as gh
+    cfg = StepConfig("long_ring", 1, 2, 1, 128, 128, 512, 1, 512 + 37, "bf16", 123)
+    cache = gh.new_gpu_cache(cfg)
+    ocache = helpers.new_oracle_cache(cfg)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    cache.kv.normal_(generator=g)
+    cache.written.fill_(True)
+    ocache.kv[...] = cache.kv.view(torch.int16).cpu().numpy().view(np.uint16)
+    ocache.written[:] = True
+    t = cfg.frame_t
+    for step, frozen in ((0, True), (1, False)):
+        q, k, v = helpers.step_inputs(cfg, t, step)
+        out = cache.append_and_attend(gh.dev_tensor(cfg, q), gh.dev_tensor(cfg, k), gh.dev_tensor(cfg, v),
+                                      gh.pos_ids(cfg, t), frozen)
+        kv_new = np.stack([helpers.to_container(cfg, k), helpers.to_container(cfg, v)], 0)
+        k_full, v_full, mask = ocache.upsert(kv_new, t, frozen)
+        assert int(mask.sum()) == cfg.L                      # 511 ring frames + the tail
+        assert gh.kv_bytes(cache) == ocache.kv.tobytes()
+        assert np.array_equal(cache.written.cpu().numpy(), ocache.written)
+        want = oracle.frame_attention(q, helpers.from_container(cfg, k_full), helpers.from_container(cfg, v_full), mask)
+        mx, mean = helpers.error_stats(out.float().cpu().numpy(), want)
+        assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"step {step}: {mx} {mean}"
+    ops.check_status(torch.device("cuda"))
