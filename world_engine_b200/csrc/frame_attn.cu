@@ -77,6 +77,15 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;    // + 128 * (tile & 1); group g owns columns [64g, 64g+64), P_g its first 32
 constexpr uint32_t kColO = 256;  // + 128 * group
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+#ifndef WE_POLY_EVERY
+#define WE_POLY_EVERY 4
+#endif
+#ifdef WE_SPIN
+#define WE_WAIT_HOT mbar_wait_spin
+#else
+#define WE_WAIT_HOT mbar_wait
+#endif
+constexpr int kPolyEvery = WE_POLY_EVERY;  // one pair of exponentials in this many runs on the FMA pipe (0: none)
 
 template <int DH>
 struct AttnCfg {
@@ -88,13 +97,13 @@ struct AttnCfg {
   static constexpr int kSmemTiles = kTileBytes * (1 + kStagesK + kStagesV);
   static constexpr int kSmemAux = 64 * 8 + kMaxTiles * 2 + 64 + 4 * kBlockM * 4 + kMaxTiles + 8 * kBlockM * 8;
   static constexpr int kSmemBytes = kSmemTiles + kSmemAux + 1024;  // + slack for 1024-byte alignment
-  // Exchange buffers of the epilogue, laid over the (then idle) rings: the CTA's partial O tile
-  // [128][DH + 4] fp32 over the K ring (4 pad columns keep the row stride off a multiple of 128 bytes), and the
-  // rows received from the other splits over the V ring.
-  static constexpr int kPartRow = DH + 4;
-  static constexpr int kPartFloats = kBlockM * kPartRow;
-  static_assert(kPartFloats * 4 <= kStagesK * kTileBytes, "the partial tile must fit in the K ring");
-  static_assert(kPartFloats * 4 <= kStagesV * kTileBytes + kPartRow * 4 * 16,
+  // Exchange buffers of the epilogue, laid over the (then idle) rings: the CTA's partial O tile over the K ring,
+  // the rows received from the other splits over the V ring.  A row travels as DH fp16 values, each half row
+  // divided by its own largest magnitude, followed by 16 bytes that hold those two magnitudes as floats (the
+  // 16 bytes also keep the row stride off a multiple of 128 bytes: no bank conflicts for 16-byte accesses).
+  static constexpr int kPartRowB = DH * 2 + 16;
+  static_assert(kBlockM * kPartRowB <= kStagesK * kTileBytes, "the partial tile must fit in the K ring");
+  static_assert(kBlockM * kPartRowB <= kStagesV * kTileBytes,
                 "the rows received from up to 7 peers (at most 7/8 of a tile) must fit in the V ring");
 };
 
@@ -135,7 +144,6 @@ struct AttnParams {
 #ifdef WE_ATTN_DEBUG
 // Debug builds only: a per-CTA timeline (SM cycles since the CTA started) written to a caller-provided buffer.
 __device__ uint32_t* g_trace = nullptr;
-__device__ int g_mode = 0;   // experiments: bit 0 = the MMA issuer does not wait for P (results are garbage)
 __device__ __forceinline__ long long trace_clock() {
   long long t;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
@@ -334,16 +342,17 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kStagesV * Cfg::kTileBytes);
   uint64_t* q_full = bars + 0;
   uint64_t* recv_bar = bars + 1;  // incoming partial rows of the split merge
-  uint64_t* s_ready = bars + 2;   // [tile & 1]
-  uint64_t* p_ready = bars + 4;   // [group][tile & 1]
-  uint64_t* o_ready = bars + 8;   // [group], one phase per tile: PV_g(i) complete
-  uint64_t* o_final = bars + 10;  // single phase: every MMA of the CTA complete
-  uint64_t* ml_bar = bars + 11;   // peers: "my main loop is over and my (m, l) rows are in your table"
-  uint64_t* ack_bar = bars + 12;  // peers: "the rows you pushed to me have landed"
-  uint64_t* k_full = bars + 13;                 // [kStagesK]
-  uint64_t* k_empty = k_full + kStagesK;        // [kStagesK]
-  uint64_t* v_full = k_empty + kStagesK;        // [kStagesV]
-  uint64_t* v_empty = v_full + kStagesV;        // [kStagesV]
+  uint64_t* ml_bar = bars + 2;    // peers: "my main loop is over and my (m, l) rows are in your table"
+  uint64_t* ack_bar = bars + 3;   // peers: "the rows you pushed to me have landed"
+  uint64_t* o_final = bars + 4;   // single phase: every MMA of the CTA complete
+  uint64_t* p_ready = bars + 5;   // [tile & 1]: all eight softmax warps have written their share of P(tile)
+  // One phase per load of the stage: S of the tile in K stage s is complete (the softmax warps may read it, the
+  // producer may refill the stage) / both PV products of the tile in V stage s are complete (O may be touched,
+  // the producer may refill the stage).  One commit of the issuing thread serves both kinds of waiter.
+  uint64_t* s_ready = bars + 7;                 // [kStagesK]
+  uint64_t* o_ready = s_ready + kStagesK;       // [kStagesV]
+  uint64_t* k_full = o_ready + kStagesV;        // [kStagesK]
+  uint64_t* v_full = k_full + kStagesK;         // [kStagesV]
   uint16_t* s_list = reinterpret_cast<uint16_t*>(bars + 64);          // [kMaxTiles] (tile << 1) | partial
   uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_list + kMaxTiles);
   uint32_t* s_tmem = s_misc + 0;
@@ -379,7 +388,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     return gv;
   };
 #ifdef WE_ATTN_DEBUG
-  const int dbg_mode = g_mode;   // read once: a global load inside the single-thread issue loop stalls the tensor pipe
   const long long t_start = trace_clock();
   uint32_t* trace = nullptr;
   {
@@ -431,13 +439,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // stream is still finishing (programmatic dependent launch).
   if (tid == 0) *s_abort = 0;
   if (warp == 8) {
-    // one barrier per lane: [0] q_full [1] recv_bar [2,3] s_ready [4..7] p_ready [8,9] o_ready [10] o_final
-    // [11] ml_bar [12] ack_bar, then the rings
-    constexpr int kNumBars = 13 + 2 * (kStagesK + kStagesV);
+    // one barrier per lane: [0] q_full [1] recv_bar [2] ml_bar [3] ack_bar [4] o_final [5,6] p_ready, then
+    // s_ready, o_ready, k_full, v_full
+    constexpr int kNumBars = 7 + 2 * (kStagesK + kStagesV);
     static_assert(kNumBars <= 32, "one lane per barrier");
     if (lane < kNumBars) {
       const int peers = p.nsplit > 1 ? p.nsplit - 1 : 1;
-      mbar_init(bars + lane, (lane >= 4 && lane < 8) ? 4 : (lane == 12 ? peers : 1));   // p_ready: one arrival per warp
+      mbar_init(bars + lane, (lane == 5 || lane == 6) ? 8 : (lane == 3 ? peers : 1));   // p_ready: one arrival per warp
     }
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
@@ -456,7 +464,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // bytes the peers will send to this CTA at the end: their (m, l) pairs and the weighted rows it owns
         const int rows_mine = (kBlockM * (split + 1)) / p.nsplit - (kBlockM * split) / p.nsplit;
         mbar_arrive_expect_tx(ml_bar, static_cast<uint32_t>((p.nsplit - 1) * kBlockM * 8));
-        mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRow * 4));
+        mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRowB));
       }
     }
     __syncwarp();
@@ -509,7 +517,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // The first tiles of the range, before it is known whether they hold a visible key (they almost always
     // do; a miss is drained later): DRAM latency then overlaps the rest of the set-up and the scan.  K(0),
     // which the first product needs, goes first.
+    WE_TRACE(11);
     if (nblind > 0) load_kv_tile(true, sK, &k_full[0], phys_tile(c0) * kBlockN);
+    WE_TRACE(12);
     if (nblind > 0) load_kv_tile(false, sV, &v_full[0], phys_tile(c0) * kBlockN);
     for (int j = 1; j < nblind; ++j) {
       const int key0 = phys_tile(c0 + j) * kBlockN;
@@ -605,6 +615,114 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   };
   if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
 
+  // Tensor products of the tiles of one parity (thread 0 of warp 9: even tiles, of warp 11: odd tiles):
+  //   S(i) = Q K(i)^T      M=128 queries, N=128 keys, K=DH in steps of 16, both operands in shared memory
+  //                        (K-major, 128-byte swizzle), into S buffer i & 1;
+  //   O_g += P_g(i) V_g(i) for the two key halves g: M=128, N=DH, K=64 keys in steps of 16; P_g sits in the first
+  //                        32 columns of group g's half of S(i) (two 16-bit values per column), V is read from
+  //                        shared memory as an MN-major operand.
+  // A thread issues S(p), then for its tiles i: P V(i) followed at once by S(i+2), which overwrites the columns of
+  // P(i): products of one thread execute in the order issued, so no barrier is needed between the two.  Issuing a
+  // product blocks the thread for about as long as the tensor pipe needs for it; with two issuing threads the
+  // waits and commits of one overlap the products of the other.  P V(i) and P V(i-1) add into the same
+  // accumulators from different threads: the later one waits for the earlier one's completion barrier.
+  auto issue_products = [&](int parity) {
+    const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16);                       // K-major, 128-byte swizzle
+    const uint32_t k_lo = umma_desc_lo(smem_u32(sK), 16);
+    const uint32_t v_lo = umma_desc_lo(smem_u32(sV), Cfg::kChunkBytes);         // MN-major: LBO = chunk stride
+    constexpr uint32_t kTileStep = Cfg::kTileBytes >> 4;
+    auto issue_s = [&](int i) {
+      const int a = load_seq(i);
+      const int sk = a % kStagesK;
+      mbar_wait(&k_full[sk], (a / kStagesK) & 1, s_abort);
+      const uint32_t d = tmem_base + kColS + 128u * (i & 1);
+      const uint32_t kb = k_lo + sk * kTileStep;
+      umma_ss_lo<0>(d, q_lo, kb, kIdescS);
+#pragma unroll
+      for (int kk = 1; kk < DH / 16; ++kk) {
+        constexpr uint32_t kChunkStep = Cfg::kChunkBytes >> 4;
+        const uint32_t off = (kk >> 2) * kChunkStep + (kk & 3) * 2;          // 32 bytes per K step
+        umma_ss_lo<1>(d, q_lo + off, kb + off, kIdescS);
+      }
+      tc_commit(&s_ready[sk]);        // the softmax warps are waiting for this one; it also frees the K stage
+    };
+#ifdef WE_ISSUE_SPLIT_KIND
+    // alternative: one thread issues every S product, the other every P V product
+    if (parity == 0) {
+      mbar_wait(q_full, 0, s_abort);
+      for (int i = 0; i < n; ++i) {
+        if (i >= 2) {
+          const int a2 = load_seq(i - 2);
+          mbar_wait(&o_ready[a2 % kStagesV], (a2 / kStagesV) & 1, s_abort);
+          tc_fence_after();
+        }
+        issue_s(i);
+      }
+    } else {
+      for (int i = 0; i < n; ++i) {
+        const int av = load_seq(i);
+        const int sv = av % kStagesV;
+        const int buf = i & 1;
+        mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
+        WE_WAIT_HOT(&p_ready[buf], (i >> 1) & 1, s_abort);
+        tc_fence_after();
+        const uint32_t vb = v_lo + sv * kTileStep;
+        const uint32_t acc0 = i > 0 ? 1u : 0u;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint32_t d = tmem_base + kColO + 128u * g;
+          const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
+        }
+        tc_commit(&o_ready[sv]);
+      }
+      tc_commit(o_final);
+    }
+    return;
+#endif
+    mbar_wait(q_full, 0, s_abort);
+    if (parity == 0) WE_TRACE(13);
+    if (parity == 0) { mbar_wait(&k_full[load_seq(0) % kStagesK], 0, s_abort); WE_TRACE(14); }
+    issue_s(parity);
+    if (parity == 0) WE_TRACE(15);
+    for (int i = parity; i < n; i += 2) {
+      const int av = load_seq(i);
+      const int sv = av % kStagesV;
+      const int buf = i & 1;
+      // everything that is ready long before P(i) is waited for first
+      mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
+      if (i + 2 < n) {
+        const int a2 = load_seq(i + 2);
+        mbar_wait(&k_full[a2 % kStagesK], (a2 / kStagesK) & 1, s_abort);
+      }
+      if (i > 0) {
+        const int ap = load_seq(i - 1);
+        mbar_wait(&o_ready[ap % kStagesV], (ap / kStagesV) & 1, s_abort);
+      }
+      if (i == 4 || i == 5) WE_TRACE(180 + 8 * (i - 4));
+      WE_WAIT_HOT(&p_ready[buf], (i >> 1) & 1, s_abort);
+      if (i == 4 || i == 5) WE_TRACE(181 + 8 * (i - 4));
+      tc_fence_after();
+      const uint32_t vb = v_lo + sv * kTileStep;
+      const uint32_t acc0 = i > 0 ? 1u : 0u;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t d = tmem_base + kColO + 128u * g;
+        const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)                                          // 16 keys = 2048 bytes of V rows
+          umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
+      }
+      tc_commit(&o_ready[sv]);        // O may be touched again, and the V stage is free
+      if (i == 4 || i == 5) WE_TRACE(182 + 8 * (i - 4));
+      if (i + 2 < n) issue_s(i + 2);
+      if (i == 4 || i == 5) WE_TRACE(183 + 8 * (i - 4));
+      if (i == n - 1) tc_commit(o_final);
+    }
+  };
+
   // ------------------------------------------------------------------ roles
   if (warp == 8 || warp == 10) {
     // Producers: warp 8 feeds the K ring, warp 10 the V ring (a ring of its own, so that a full V ring never
@@ -613,7 +731,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const bool is_k = warp == 8;
       uint8_t* ring = is_k ? sK : sV;
       uint64_t* full = is_k ? k_full : v_full;
-      uint64_t* empty = is_k ? k_empty : v_empty;
+      uint64_t* empty = is_k ? s_ready : o_ready;
       const int stages = is_k ? kStagesK : kStagesV;
       const int nloads = nblind + n - n_vis_blind;
       const bool to_ring = !p.is_frozen && hide_i;
@@ -662,78 +780,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int j = 0; j < nblind; ++j) {
         if (!((blind_vis >> j) & 1u)) {
           mbar_wait(&k_full[j], 0, s_abort);
-          mbar_arrive(&k_empty[j]);
+          mbar_arrive(&s_ready[j]);
           mbar_wait(&v_full[j], 0, s_abort);
-          mbar_arrive(&v_empty[j]);
+          mbar_arrive(&o_ready[j]);
         }
       }
     }
-    if (lane == 0 && n > 0) {
-      // Low descriptor words of the operand tiles; a step of 16 along K adds a constant.
-      const uint32_t q_lo = umma_desc_lo(smem_u32(sQ), 16);                       // K-major, 128-byte swizzle
-      const uint32_t k_lo = umma_desc_lo(smem_u32(sK), 16);
-      const uint32_t v_lo = umma_desc_lo(smem_u32(sV), Cfg::kChunkBytes);         // MN-major: LBO = chunk stride
-      constexpr uint32_t kTileStep = Cfg::kTileBytes >> 4;
-      mbar_wait(q_full, 0, s_abort);
-      // S(i) = Q K(i)^T : M=128 queries, N=128 keys, K=DH in steps of 16; into S buffer i & 1.
-      // (The wait for the K tile stays right in front of the products: waiting for it a tile earlier, while the
-      // pipe is busy, was measured slower -- the K ring of 3 stages is not that far ahead under load.)
-      auto issue_s = [&](int i) {
-        const int a = load_seq(i);
-        const int sk = a % kStagesK;
-        mbar_wait(&k_full[sk], (a / kStagesK) & 1, s_abort);
-        tc_fence_after();
-        const uint32_t d = tmem_base + kColS + 128u * (i & 1);
-        const uint32_t kb = k_lo + sk * kTileStep;
-        umma_ss_lo<0>(d, q_lo, kb, kIdescS);
-#pragma unroll
-        for (int kk = 1; kk < DH / 16; ++kk) {
-          constexpr uint32_t kChunkStep = Cfg::kChunkBytes >> 4;
-          const uint32_t off = (kk >> 2) * kChunkStep + (kk & 3) * 2;          // 32 bytes per K step
-          umma_ss_lo<1>(d, q_lo + off, kb + off, kIdescS);
-        }
-        tc_commit(&s_ready[i & 1]);     // the softmax warps are waiting for this one
-        tc_commit(&k_empty[sk]);
-      };
-      WE_TRACE_MMA(9);
-      issue_s(0);
-      WE_TRACE_MMA(10);
-      for (int i = 0; i < n; ++i) {
-        const int av = load_seq(i);
-        const int sv = av % kStagesV;
-        const int buf = i & 1;
-        // S(i+1) goes first: its buffer was released when both halves of P(i-1) were consumed, and the
-        // tensor pipe computes it while the softmax warps are busy with S(i).
-        if (i < 8) WE_TRACE_MMA(96 + 6 * i);
-        if (i + 1 < n) issue_s(i + 1);
-        if (i < 8) WE_TRACE_MMA(97 + 6 * i);
-        mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);   // landed long ago as a rule
-        // O_g += P_g(i) V_g(i) for the two key halves g of the tile: M=128 queries, N=DH, K=64 keys in
-        // steps of 16.  P_g sits in the first 32 columns of group g's half of S (two bf16 per column).
-        const uint32_t vb = v_lo + sv * kTileStep;
-        const uint32_t acc0 = i > 0 ? 1u : 0u;
-#ifdef WE_ATTN_DEBUG
-        if (!(dbg_mode & 1))
-#endif
-        {
-          mbar_wait(&p_ready[0 * 2 + buf], (i >> 1) & 1, s_abort);
-          mbar_wait(&p_ready[1 * 2 + buf], (i >> 1) & 1, s_abort);
-        }
-        tc_fence_after();
-        // one burst of eight products: every wait, fence or commit between two products is a bubble in the pipe
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint32_t d = tmem_base + kColO + 128u * g;
-          const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)                                          // 16 keys = 2048 bytes of V rows
-            umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
-          tc_commit(&o_ready[g]);
-        }
-        tc_commit(&v_empty[sv]);
-      }
-      tc_commit(o_final);
-    }
+    if (lane == 0 && n > 0) issue_products(0);
     __syncwarp();
   } else if (warp < 8) {
     // ------------------------------------------------------- softmax warps
@@ -755,21 +808,15 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < n; ++i) {
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
-      mbar_wait(&s_ready[buf], (i >> 1) & 1, s_abort);
-      if (row == 0 && i < 32 && (kFullTrace || i == 1 || i == n - 1)) WE_TRACE(16 + 4 * i + 2 * wg);
-#ifdef WE_ATTN_DEBUG
-      if (dbg_mode & 2) {   // experiment: no softmax work at all, only the hand-over
-        if (i > 0) mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_ready[wg * 2 + buf]);
-        continue;
-      }
-#endif
+      const int a_i = load_seq(i);
+      WE_WAIT_HOT(&s_ready[a_i % kStagesK], (a_i / kStagesK) & 1, s_abort);
+      if (row == 0 && i < 32 && (kFullTrace || i == 1 || i == 4 || i == 5 || i == n - 1)) WE_TRACE(16 + 4 * i + 2 * wg);
       tc_fence_after();
       uint32_t s[2][32];
       tmem_ld32(s_addr, s[0]);
       tmem_ld32(s_addr + 32, s[1]);
       tmem_ld_wait();
+      if (row == 0 && i == 4) WE_TRACE(200 + 4 * wg + 0);
       if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 0);
       const uint32_t entry = s_list[t0 + i];
       if (entry & 1u) {
@@ -805,24 +852,52 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         l_run *= alpha;
         m_run = m_new;
       }
-      // P = exp2(S * scale - m): the argument on packed fp32 pairs (one FMA per pair), one ex2.approx per element.
-      // Measured alternatives, all slower with the packed arithmetic in place: a share of the exponentials as
-      // a cubic polynomial on the FMA pipe (costs more issue slots than it frees on the special-function pipe;
-      // 13 of 32 pairs: +3 %), ex2 on packed bf16 pairs (+5 %, and twice the error).
+      // P = exp2(S * scale - m): the argument on packed fp32 pairs (one FMA per pair).  The special-function
+      // pipe (16 ex2 per clock and SM) is what bounds this loop, so one pair in kPolyEvery is evaluated on the
+      // FMA pipe instead: round to the nearest integer n with the 1.5 * 2^23 trick, a cubic in x - n (relative
+      // error 7.5e-5, far below the rounding of P to 16 bits), n added into the exponent field.  Tiles with
+      // masked keys (scores of -inf) take the special-function pipe for every element.
+      if (row == 0 && i == 4) WE_TRACE(200 + 4 * wg + 1);
       const uint64_t scale2 = splat2(p.scale_log2), negm2 = splat2(-m_run);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t pk[32];
+      auto exponentials = [&](auto poly_c) {
+        constexpr bool kPoly = decltype(poly_c)::value;
+        const uint64_t magic2 = splat2(12582912.f), nmagic2 = splat2(-12582912.f), mone2 = splat2(-1.f);
+        const uint64_t c0 = splat2(0.9999280571937561f), c1 = splat2(0.6932609677314758f),
+                       c2 = splat2(0.2426111251115799f), c3 = splat2(0.05517164617776871f);
 #pragma unroll
-      for (int q = 0; q < 32; ++q) {
-        const int c = q >> 4, e = q & 15;
-        const uint64_t x2 = fma2(pk64(s[c][2 * e], s[c][2 * e + 1]), scale2, negm2);
-        uint32_t xl, xh;
-        upk64(x2, xl, xh);
-        const uint32_t pl = __float_as_uint(fast_exp2(__uint_as_float(xl)));
-        const uint32_t ph = __float_as_uint(fast_exp2(__uint_as_float(xh)));
-        sum2[q & 3] = add2(sum2[q & 3], pk64(pl, ph));
-        pk[q] = pack2<BF16>(__uint_as_float(pl), __uint_as_float(ph));
-      }
+        for (int q = 0; q < 32; ++q) {
+          const int c = q >> 4, e = q & 15;
+          const uint64_t x2 = fma2(pk64(s[c][2 * e], s[c][2 * e + 1]), scale2, negm2);
+          uint32_t pl, ph;
+          if (kPoly && kPolyEvery > 0 && (q % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery > 0 ? kPolyEvery : 1) - 1) {
+            const uint64_t t2 = add2(x2, magic2);
+            const uint64_t n2 = add2(t2, nmagic2);
+            const uint64_t f2 = fma2(n2, mone2, x2);
+            uint64_t p2 = fma2(c3, f2, c2);
+            p2 = fma2(p2, f2, c1);
+            p2 = fma2(p2, f2, c0);
+            uint32_t tl, th;
+            upk64(t2, tl, th);
+            upk64(p2, pl, ph);
+            // exponent: n >= -126 (as integers the bit patterns of t order like the values; t < 0 reads negative)
+            constexpr int kMinT = 0x4B400000 - 126;
+            pl += static_cast<uint32_t>(max(static_cast<int>(tl), kMinT)) << 23;
+            ph += static_cast<uint32_t>(max(static_cast<int>(th), kMinT)) << 23;
+          } else {
+            uint32_t xl, xh;
+            upk64(x2, xl, xh);
+            pl = __float_as_uint(fast_exp2(__uint_as_float(xl)));
+            ph = __float_as_uint(fast_exp2(__uint_as_float(xh)));
+          }
+          sum2[q & 3] = add2(sum2[q & 3], pk64(pl, ph));
+          pk[q] = pack2<BF16>(__uint_as_float(pl), __uint_as_float(ph));
+        }
+      };
+      if (entry & 1u) exponentials(std::false_type{});
+      else exponentials(std::true_type{});
+      if (row == 0 && i == 4) WE_TRACE(200 + 4 * wg + 2);
       float sum4[4];
       {
         const uint64_t t01 = add2(sum2[0], sum2[1]), t23 = add2(sum2[2], sum2[3]);
@@ -837,13 +912,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tmem_st32(s_addr, pk);                                    // P over the S columns this thread has consumed
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (kFullTrace && row == 0 && i < 32) WE_TRACE(17 + 4 * i + 2 * wg);
-      if (i > 0) {
-        // PV_g(i-1) has long been issued; its completion makes O_g safe to touch and is awaited every tile so
-        // that no phase of the barrier is ever skipped.
-      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 4);
-        mbar_wait(&o_ready[wg], (i - 1) & 1, s_abort);
-      if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 5);
-        if (raise) {
+      if (i > 0 && raise) {
+        // O_g is rescaled in place: PV(i-1) must have completed.  (Waiting only here is safe: the phase after
+        // this one on the same barrier belongs to PV(i+1), which cannot complete before P(i+1) exists.)
+        const int a_p = load_seq(i - 1);
+        mbar_wait(&o_ready[a_p % kStagesV], (a_p / kStagesV) & 1, s_abort);
+        {
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < DH / 32; ++c) {
@@ -857,11 +931,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       tmem_st_wait();
+      if (row == 0 && i == 4) WE_TRACE(200 + 4 * wg + 3);
       if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 6);
       tc_fence_before();
       // one arrival per warp: 128 separate arrivals on one barrier word would queue up behind one another
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[wg * 2 + buf]);
+      if (lane == 0) mbar_arrive(&p_ready[buf]);
       if (kFullTrace && row == 0 && i == 3) WE_TRACE(160 + 8 * wg + 7);
     }
 
@@ -938,10 +1013,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
       } else {
-        // this split's rows, relative to its own maximum m_cta and not yet normalised: fp32, in the (idle) K ring
-        float* part = reinterpret_cast<float*>(sK);
-        const float wa = w_g0 * wgt, wb = w_g1 * wgt;
-#pragma unroll 1
+        // This split's rows, relative to its own maximum m_cta and not yet normalised, staged in the (idle) K ring
+        // as fp16: every half row is divided by its largest magnitude first, so the values lie in [-1, 1] whatever
+        // the range of V, and the rounding error (2^-12 of that magnitude) is far below the 2^-9 of the output's
+        // own rounding.  Half as many bytes cross between the SMs as with fp32 rows.
+        uint8_t* part = sK;
+        const float wa = w_g0, wb = w_g1;
+        float f[kHalf];
+#pragma unroll
         for (int c = 0; c < kHalf / 32; ++c) {
           uint32_t oa[32], ob[32];
           if (n > 0) {
@@ -949,35 +1028,44 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             tmem_ld32(o1_addr + c * 32, ob);
             tmem_ld_wait();
           }
-          float4* dst = reinterpret_cast<float4*>(part + row * Cfg::kPartRow + col0 + c * 32);
           if (n > 0 && wa != 0.f && wb != 0.f) {
             // both streams contribute (the usual case): packed pairs, two instructions per pair
             const uint64_t wa2 = splat2(wa), wb2 = splat2(wb);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const uint64_t lo = fma2(pk64(oa[4 * e + 0], oa[4 * e + 1]), wa2,
-                                       fma2(pk64(ob[4 * e + 0], ob[4 * e + 1]), wb2, 0ull));
-              const uint64_t hi = fma2(pk64(oa[4 * e + 2], oa[4 * e + 3]), wa2,
-                                       fma2(pk64(ob[4 * e + 2], ob[4 * e + 3]), wb2, 0ull));
-              uint32_t x, y, z, w;
-              upk64(lo, x, y);
-              upk64(hi, z, w);
-              dst[e] = make_float4(__uint_as_float(x), __uint_as_float(y), __uint_as_float(z), __uint_as_float(w));
+            for (int e = 0; e < 16; ++e) {
+              const uint64_t t = fma2(pk64(oa[2 * e], oa[2 * e + 1]), wa2, fma2(pk64(ob[2 * e], ob[2 * e + 1]), wb2, 0ull));
+              uint32_t x, y;
+              upk64(t, x, y);
+              f[c * 32 + 2 * e] = __uint_as_float(x);
+              f[c * 32 + 2 * e + 1] = __uint_as_float(y);
             }
           } else {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (n > 0) {
-                v.x = merge2(__uint_as_float(oa[4 * e + 0]), wa, __uint_as_float(ob[4 * e + 0]), wb);
-                v.y = merge2(__uint_as_float(oa[4 * e + 1]), wa, __uint_as_float(ob[4 * e + 1]), wb);
-                v.z = merge2(__uint_as_float(oa[4 * e + 2]), wa, __uint_as_float(ob[4 * e + 2]), wb);
-                v.w = merge2(__uint_as_float(oa[4 * e + 3]), wa, __uint_as_float(ob[4 * e + 3]), wb);
-              }
-              dst[e] = v;
-            }
+            for (int e = 0; e < 32; ++e)
+              f[c * 32 + e] = n > 0 ? merge2(__uint_as_float(oa[e]), wa, __uint_as_float(ob[e]), wb) : 0.f;
           }
         }
+        float am4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int e = 0; e < kHalf; e += 8) {
+          am4[0] = max3(am4[0], fabsf(f[e + 0]), fabsf(f[e + 1]));
+          am4[1] = max3(am4[1], fabsf(f[e + 2]), fabsf(f[e + 3]));
+          am4[2] = max3(am4[2], fabsf(f[e + 4]), fabsf(f[e + 5]));
+          am4[3] = max3(am4[3], fabsf(f[e + 6]), fabsf(f[e + 7]));
+        }
+        const float amax = fmaxf(fmaxf(am4[0], am4[1]), fmaxf(am4[2], am4[3]));
+        const float ainv = amax > 0.f ? __fdividef(1.0f, amax) : 0.f;
+        uint8_t* prow = part + row * Cfg::kPartRowB;
+#pragma unroll
+        for (int e = 0; e < kHalf / 8; ++e) {
+          uint4 v;
+          v.x = pack2<false>(f[8 * e + 0] * ainv, f[8 * e + 1] * ainv);
+          v.y = pack2<false>(f[8 * e + 2] * ainv, f[8 * e + 3] * ainv);
+          v.z = pack2<false>(f[8 * e + 4] * ainv, f[8 * e + 5] * ainv);
+          v.w = pack2<false>(f[8 * e + 6] * ainv, f[8 * e + 7] * ainv);
+          *reinterpret_cast<uint4*>(prow + wg * kHalf * 2 + e * 16) = v;
+        }
+        *reinterpret_cast<float*>(prow + DH * 2 + 4 * wg) = amax;
         fence_proxy_async_smem();        // the rows are read by bulk copies (async proxy) below
       }
       if (row == 0) WE_TRACE(234 + wg);
@@ -1057,6 +1145,13 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint8_t* w = p.written_w + b * p.written_batch_stride + slot_base;
       for (int t = lane; t < p.T; t += 32) w[t] = 1;
     }
+    // ... and its first lane issues the tensor products of the odd tiles
+#ifdef WE_ISSUE_SPLIT_KIND
+    if (lane == 0 && n > 0) issue_products(1);
+#else
+    if (lane == 0 && n > 1) issue_products(1);
+#endif
+    __syncwarp();
   }
 
   // ------------------------------------------------ merge of the splits through cluster shared memory
@@ -1066,47 +1161,43 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // order, so reruns are bit-identical.
   if (p.cluster_merge && p.nsplit > 1 && warp < 8) {
     // Only the 256 threads that staged the rows take part: a barrier among them, not the whole CTA.
-    const int ns = p.nsplit;
-    const int r0 = (kBlockM * split) / ns, r1 = (kBlockM * (split + 1)) / ns;
-    const int R = r1 - r0;
-    float* part = reinterpret_cast<float*>(sK);
-    float* recv = reinterpret_cast<float*>(sV);
-    const int slot_floats = R * Cfg::kPartRow;
-    if (lane == 0) WE_TRACE(244 + warp);
-    named_bar_sync(1, kSoftmaxThreads);           // this CTA's rows are staged
-    // One courier thread per peer (lane 0 of warp `peer`) sends that peer its rows and, once this CTA's own
-    // inbox is full, the acknowledgement.
-    const int tpr = kSoftmaxThreads / R;          // threads per row in the sum below (2 ns)
-    const int rl = tid / tpr;
-    const int cg0 = tid - rl * tpr;
-    const bool courier = lane == 0 && warp < ns && warp != split;
-    if (tid == 0) WE_TRACE(236);
-    if (courier) {
-      const int d = warp;
-      // once all peers' pairs are here their main loops are over, so their V rings may be written
-      mbar_wait(ml_bar, 0, s_abort);
-      const int d0 = (kBlockM * d) / ns, d1 = (kBlockM * (d + 1)) / ns;
-      const int my_slot = split < d ? split : split - 1;          // my position among d's peers
-      const uint32_t dst = dsmem_addr(smem_u32(sV) + static_cast<uint32_t>(my_slot * (d1 - d0) * Cfg::kPartRow * 4),
-                                      static_cast<uint32_t>(d));
-      const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
-      bulk_copy_to_peer(dst, smem_u32(part + d0 * Cfg::kPartRow), static_cast<uint32_t>((d1 - d0) * Cfg::kPartRow * 4),
-                        bar);
-    }
-    // (asynchronous stores and bulk copies complete on the barrier through the async proxy, like any TMA
-    // copy: the ordinary wait of the receiving CTA orders the data)
-    mbar_wait(ml_bar, 0, s_abort);           // all pairs present
-    if (tid == 0) WE_TRACE(242);
-    // 2 * ns threads share one of the R = 128 / ns rows; each takes every (2 ns)-th group of 4 columns (eight
-    // neighbouring lanes read one 128-byte line: no bank conflicts).  Split
-    // u's row enters with the weight exp2(m_u - m_row) / l_row, l_row = sum over splits of l_u exp2(m_u - m_row),
-    // computed once per thread.  Compiled once per split count, so that no loop carries dead iterations.
-    auto sum_rows = [&](auto ns_const) {
+    // Compiled once per split count, so that every division is by a constant and no loop carries dead iterations.
+    auto merge_splits = [&](auto ns_const) {
       constexpr int NS = decltype(ns_const)::value;
-      constexpr int kGroups = DH / 4;
-      constexpr int kTpr = 2 * NS;                                  // = kSoftmaxThreads / (kBlockM / NS)
-      constexpr int kMaxIt = kGroups / kTpr;
-      static_assert(kGroups % kTpr == 0, "every thread takes the same number of column groups");
+      constexpr int R = kBlockM / NS;                     // rows this CTA owns
+      constexpr int kRowB = Cfg::kPartRowB;
+      constexpr int kTpr = 2 * NS;                        // threads per owned row in the sum (256 / R)
+      constexpr int kGroups = DH / 8;                     // groups of 8 columns = 16 bytes of fp16
+      constexpr int kIt = kGroups >= kTpr ? kGroups / kTpr : 1;
+      constexpr int kGroupsPerHalf = kGroups / 2;
+      const int r0 = R * split;
+      uint8_t* part = sK;
+      uint8_t* recv = sV;
+      if (lane == 0) WE_TRACE(244 + warp);
+      named_bar_sync(1, kSoftmaxThreads);           // this CTA's rows are staged
+      // One courier thread per peer (lane 0 of warp `peer`) sends that peer its rows and, once this CTA's own
+      // inbox is full, the acknowledgement.
+      const int rl = tid / kTpr;
+      const int cg0 = tid % kTpr;
+      const bool courier = lane == 0 && warp < NS && warp != split;
+      if (tid == 0) WE_TRACE(236);
+      if (courier) {
+        const int d = warp;
+        // once all peers' pairs are here their main loops are over, so their V rings may be written
+        mbar_wait(ml_bar, 0, s_abort);
+        const int my_slot = split < d ? split : split - 1;          // my position among d's peers
+        const uint32_t dst = dsmem_addr(smem_u32(recv) + static_cast<uint32_t>(my_slot * R * kRowB),
+                                        static_cast<uint32_t>(d));
+        const uint32_t bar = dsmem_addr(smem_u32(recv_bar), static_cast<uint32_t>(d));
+        bulk_copy_to_peer(dst, smem_u32(part + d * R * kRowB), static_cast<uint32_t>(R * kRowB), bar);
+      }
+      // (asynchronous stores and bulk copies complete on the barrier through the async proxy, like any TMA
+      // copy: the ordinary wait of the receiving CTA orders the data)
+      mbar_wait(ml_bar, 0, s_abort);           // all pairs present
+      if (tid == 0) WE_TRACE(242);
+      // 2 NS threads share one of the R = 128 / NS rows; each takes every (2 NS)-th group of 8 columns (eight
+      // neighbouring lanes read one 128-byte line: no bank conflicts).  Split u's half row enters with the weight
+      // exp2(m_u - m_row) / l_row times its magnitude, l_row = sum over splits of l_u exp2(m_u - m_row).
       const int row = r0 + rl;
       float w_u[NS], l_u[NS];
       float m_all = -INFINITY;
@@ -1134,44 +1225,50 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint8_t* orow = static_cast<uint8_t*>(p.out) +
                       2 * (b * p.os[0] + h * p.os[1] + static_cast<int64_t>(q0 + row) * p.os[2]);
       const bool in_range = q0 + row < p.T;
-      // all loads first, then the stores: nothing orders them behind one another
-      float4 acc[kMaxIt];
+      const bool active = cg0 < kGroups;       // (more threads than column groups only at DH = 64 with 8 splits)
+      float acc[kIt][8];
 #pragma unroll
-      for (int k = 0; k < kMaxIt; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < kIt; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[k][e] = 0.f;
 #pragma unroll
       for (int u = 0; u < NS; ++u) {
-        const float* src = u == split ? part + row * Cfg::kPartRow
-                                      : recv + (u < split ? u : u - 1) * slot_floats + rl * Cfg::kPartRow;
-        const float w = w_u[u];
+        const uint8_t* src = u == split ? part + row * kRowB : recv + ((u < split ? u : u - 1) * R + rl) * kRowB;
+        const float2 mag = *reinterpret_cast<const float2*>(src + DH * 2);
+        const float w0 = w_u[u] * mag.x, w1 = w_u[u] * mag.y;
 #pragma unroll
-        for (int k = 0; k < kMaxIt; ++k) {
+        for (int k = 0; k < kIt; ++k) {
           const int cg = cg0 + k * kTpr;
-          {
-            const float4 v = *reinterpret_cast<const float4*>(src + cg * 4);
-            acc[k].x = fmaf(w, v.x, acc[k].x);
-            acc[k].y = fmaf(w, v.y, acc[k].y);
-            acc[k].z = fmaf(w, v.z, acc[k].z);
-            acc[k].w = fmaf(w, v.w, acc[k].w);
+          if (active) {
+            const float w = cg < kGroupsPerHalf ? w0 : w1;
+            const uint4 v = *reinterpret_cast<const uint4*>(src + cg * 16);
+            const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&vv[e]));
+              acc[k][2 * e + 0] = fmaf(w, x.x, acc[k][2 * e + 0]);
+              acc[k][2 * e + 1] = fmaf(w, x.y, acc[k][2 * e + 1]);
+            }
           }
         }
       }
       if (tid == 0) WE_TRACE(243);
-      if (in_range) {
+      if (in_range && active) {
 #pragma unroll
-        for (int k = 0; k < kMaxIt; ++k) {
+        for (int k = 0; k < kIt; ++k) {
           const int cg = cg0 + k * kTpr;
-          {
-            uint2 v2;
-            v2.x = pack2<BF16>(acc[k].x, acc[k].y);
-            v2.y = pack2<BF16>(acc[k].z, acc[k].w);
-            *reinterpret_cast<uint2*>(orow + cg * 8) = v2;
-          }
+          uint4 v;
+          v.x = pack2<BF16>(acc[k][0], acc[k][1]);
+          v.y = pack2<BF16>(acc[k][2], acc[k][3]);
+          v.z = pack2<BF16>(acc[k][4], acc[k][5]);
+          v.w = pack2<BF16>(acc[k][6], acc[k][7]);
+          *reinterpret_cast<uint4*>(orow + cg * 16) = v;
         }
       }
     };
-    if (ns == 2) sum_rows(std::integral_constant<int, 2>{});
-    else if (ns == 4) sum_rows(std::integral_constant<int, 4>{});
-    else sum_rows(std::integral_constant<int, 8>{});
+    if (p.nsplit == 2) merge_splits(std::integral_constant<int, 2>{});
+    else if (p.nsplit == 4) merge_splits(std::integral_constant<int, 4>{});
+    else merge_splits(std::integral_constant<int, 8>{});
     if (tid == 0) WE_TRACE(238);
     if (tid == kAttnThreads - 1) WE_TRACE(241);
     // This CTA may leave once every peer has acknowledged the rows pushed to it; nothing else of this CTA is
@@ -1494,9 +1591,6 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
 }  // namespace we
 
 #ifdef WE_ATTN_DEBUG
-extern "C" __attribute__((visibility("default"))) int we_b200_debug_mode(int mode) {
-  return static_cast<int>(cudaMemcpyToSymbol(we::g_mode, &mode, sizeof(mode)));
-}
 // Buffer of 64 x 256 uint32 for the per-CTA timeline (null switches tracing off).
 extern "C" __attribute__((visibility("default"))) int we_b200_debug_trace(uint32_t* buf) {
   return static_cast<int>(cudaMemcpyToSymbol(we::g_trace, &buf, sizeof(buf)));
