@@ -80,11 +80,6 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #ifndef WE_POLY_EVERY
 #define WE_POLY_EVERY 4
 #endif
-#ifdef WE_SPIN
-#define WE_WAIT_HOT mbar_wait_spin
-#else
-#define WE_WAIT_HOT mbar_wait
-#endif
 constexpr int kPolyEvery = WE_POLY_EVERY;  // one pair of exponentials in this many runs on the FMA pipe (0: none)
 
 template <int DH>
@@ -120,6 +115,9 @@ struct AttnParams {
   int32_t ntiles;                // ceil(C / 128)
   int32_t ring_frames;           // L / T
   int32_t nsplit, n_qtiles;
+  int32_t log2_nsplit;           // nsplit is a power of two
+  int32_t gqa;                   // query heads per kv head
+  int32_t hid_tiles_max;         // T / 128: the most whole key tiles a hidden slot can cover
   int32_t q_perm[3];             // which of (t, h, b) feeds tensor-map coordinate 1, 2, 3
   int32_t kv_perm[3];
   float scale_log2;
@@ -291,9 +289,14 @@ __device__ __forceinline__ void slot_of_fast(int64_t ft, int64_t L, int T, int d
                                              int& hide) {
   if (static_cast<uint64_t>(ft) < 0x3FFFFFFFull) {
     const uint32_t t = static_cast<uint32_t>(ft), d = static_cast<uint32_t>(dilation);
-    const uint32_t buckets = static_cast<uint32_t>(ring_frames) / d;
-    slot_base = static_cast<int>((((t + d - 1u) / d) % buckets) * static_cast<uint32_t>(T));
-    hide = (t % d) == 0u;
+    if (d == 1u) {                                  // the common case: one division instead of three
+      slot_base = static_cast<int>((t % static_cast<uint32_t>(ring_frames)) * static_cast<uint32_t>(T));
+      hide = 1;
+    } else {
+      const uint32_t buckets = static_cast<uint32_t>(ring_frames) / d;
+      slot_base = static_cast<int>((((t + d - 1u) / d) % buckets) * static_cast<uint32_t>(T));
+      hide = (t % d) == 0u;
+    }
   } else {
     const SlotInfo si = slot_of(ft, L, T, dilation);
     slot_base = static_cast<int>(si.base);
@@ -368,11 +371,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int split = blockIdx.x % p.nsplit;   // consecutive blocks = the splits of one query tile (one cluster)
-  const int qt = blockIdx.x / p.nsplit;
+  const int split = blockIdx.x & (p.nsplit - 1);   // consecutive blocks = the splits of one query tile (one cluster)
+  const int qt = blockIdx.x >> p.log2_nsplit;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
-  const int kvh = h / (p.Hq / p.Hkv);
+  const int kvh = p.gqa == 1 ? h : h / p.gqa;
   const int q0 = qt * kBlockM;
   const uint8_t* wr = p.written + static_cast<int64_t>(b) * p.written_batch_stride;
   // Factor of output row `r` of this tile: 1, or the head gate (sigmoid of the logit, rounded to the tensors'
@@ -421,7 +424,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // tiles of the new frame that pass through their rings: one tensor store from shared memory into the tail
   // slice and, on an unfrozen write step, one into the ring slot (LayerKVCache.upsert,
   // src/model/kv_cache.py:138,147-150).  The stores un-swizzle on the way out, like the loads swizzled.
-  const bool storer = p.fused && qt == 0 && h == kvh * (p.Hq / p.Hkv);
+  const bool storer = p.fused && qt == 0 && h == kvh * p.gqa;
   auto store_kv_tile = [&](bool is_k, const uint8_t* src, int key0, bool to_ring, int slot_base) {
     const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
 #pragma unroll 1
@@ -462,7 +465,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       fence_proxy_async_smem();
       if (p.cluster_merge && p.nsplit > 1) {
         // bytes the peers will send to this CTA at the end: their (m, l) pairs and the weighted rows it owns
-        const int rows_mine = (kBlockM * (split + 1)) / p.nsplit - (kBlockM * split) / p.nsplit;
+        const int rows_mine = kBlockM >> p.log2_nsplit;
         mbar_arrive_expect_tx(ml_bar, static_cast<uint32_t>((p.nsplit - 1) * kBlockM * 8));
         mbar_arrive_expect_tx(recv_bar, static_cast<uint32_t>((p.nsplit - 1) * rows_mine * Cfg::kPartRowB));
       }
@@ -490,6 +493,16 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
     for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(sQ + ch * Cfg::kChunkBytes, &tm_q, q_full, ch * 64, x1, x2, x3);
   }
+  // The visibility scan is done by every warp but the producer (warp 8), which fetches tiles meanwhile.  Its loads
+  // of `written` go out before the frame counter is known, for every physical tile this CTA can possibly be
+  // given: candidate ranges move by at most the tiles of one hidden slot.
+  constexpr int kScanThreads = kAttnThreads - 32;
+  const int stid = tid < 256 ? tid : tid - 32;
+  const int c0_min = ((p.ntiles - p.hid_tiles_max) * split) >> p.log2_nsplit;
+  int span = ((p.ntiles * (split + 1)) >> p.log2_nsplit) + p.hid_tiles_max - c0_min;
+  span = min(span, p.ntiles - c0_min);
+  const int my_j = stid >> 3;
+  const uint4 w_first = load_written16(wr, my_j < span ? (c0_min + my_j) * 8 + (stid & 7) : 0x3FFFFFF, p.C);
   // Candidate tiles = physical tiles minus those that lie entirely in the hidden slot (pure arithmetic on
   // the frame counter).  Split `split` owns candidates [c0, c1); which of them hold a visible key is decided
   // below from `written`.
@@ -501,18 +514,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int last_h = hide_i ? (slot_base + p.T) / kBlockN : 0;
   const int count_h = last_h > first_h ? last_h - first_h : 0;
   const int n_cand = p.ntiles - count_h;
-  const int c0 = static_cast<int>((static_cast<int64_t>(n_cand) * split) / p.nsplit);
-  const int c1 = static_cast<int>((static_cast<int64_t>(n_cand) * (split + 1)) / p.nsplit);
+  const int c0 = (n_cand * split) >> p.log2_nsplit;
+  const int c1 = (n_cand * (split + 1)) >> p.log2_nsplit;
   const int np = c1 - c0;
   auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
   constexpr int kBlind = 2;                       // tiles loaded before their visibility is known
   const int nblind = np < kBlind ? np : kBlind;
-  // The visibility scan is done by every warp but the producer (warp 8), which fetches tiles meanwhile.
-  constexpr int kScanThreads = kAttnThreads - 32;
-  const int stid = tid < 256 ? tid : tid - 32;
-  // this thread's first 16 tokens of `written` (of its candidate range), in flight during the set-up
-  const int my_j = stid >> 3;
-  const uint4 w_first = load_written16(wr, my_j < np ? phys_tile(c0 + my_j) * 8 + (stid & 7) : 0x3FFFFFF, p.C);
   if (warp == 8 && lane == 0) {
     // The first tiles of the range, before it is known whether they hold a visible key (they almost always
     // do; a miss is drained later): DRAM latency then overlaps the rest of the set-up and the scan.  K(0),
@@ -552,11 +559,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       s_slot[0] = slot_base;
       s_slot[1] = hide_i;
     }
-    const int nvec_pad = (np * 8 + 31) & ~31;      // whole warps take part in the shuffles
+    const int nvec_pad = (span * 8 + 31) & ~31;    // whole warps take part in the shuffles
 #pragma unroll 1
     for (int idx = stid; idx < nvec_pad; idx += kScanThreads) {
-      const int j = idx >> 3;
-      const int v = j < np ? phys_tile(c0 + j) * 8 + (idx & 7) : 0x3FFFFFF;
+      const int j = idx >> 3;                        // physical tile c0_min + j
+      const int v = j < span ? (c0_min + j) * 8 + (idx & 7) : 0x3FFFFFF;
       uint4 w = w_first;
       if (idx != stid) w = load_written16(wr, v, p.C);
       const int k0 = v * 16;
@@ -565,7 +572,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint32_t nz2 = __vcmpne4(w.z, 0u) & 0x01010101u, nz3 = __vcmpne4(w.w, 0u) & 0x01010101u;
       int cnt = __popc(nz0) + __popc(nz1) + __popc(nz2) + __popc(nz3);
       const int lo = max(k0, hid_lo), hi = min(k0 + 16, hid_hi);
-      if (j < np && lo < hi) {
+      if (j < span && lo < hi) {
         if (lo == k0 && hi == k0 + 16) {
           cnt = 0;                                   // the whole vector lies in the hidden slot
         } else {
@@ -576,14 +583,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
       cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
-      if ((lane & 7) == 0 && j < np) s_cnt[j] = static_cast<uint8_t>(cnt);
+      if ((lane & 7) == 0 && j < span) s_cnt[j] = static_cast<uint8_t>(cnt);
     }
     named_bar_sync(3, kScanThreads);
     if (warp == 11) {
 #pragma unroll 1
       for (int base = 0; base < np; base += 32) {
         const int j = base + lane;
-        const int c = j < np ? s_cnt[j] : 0;
+        const int c = j < np ? s_cnt[phys_tile(c0 + j) - c0_min] : 0;
         const unsigned m = __ballot_sync(0xffffffffu, c != 0);
         if (c != 0)
           s_list[n + __popc(m & ((1u << lane) - 1u))] =
@@ -646,42 +653,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tc_commit(&s_ready[sk]);        // the softmax warps are waiting for this one; it also frees the K stage
     };
-#ifdef WE_ISSUE_SPLIT_KIND
-    // alternative: one thread issues every S product, the other every P V product
-    if (parity == 0) {
-      mbar_wait(q_full, 0, s_abort);
-      for (int i = 0; i < n; ++i) {
-        if (i >= 2) {
-          const int a2 = load_seq(i - 2);
-          mbar_wait(&o_ready[a2 % kStagesV], (a2 / kStagesV) & 1, s_abort);
-          tc_fence_after();
-        }
-        issue_s(i);
-      }
-    } else {
-      for (int i = 0; i < n; ++i) {
-        const int av = load_seq(i);
-        const int sv = av % kStagesV;
-        const int buf = i & 1;
-        mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
-        WE_WAIT_HOT(&p_ready[buf], (i >> 1) & 1, s_abort);
-        tc_fence_after();
-        const uint32_t vb = v_lo + sv * kTileStep;
-        const uint32_t acc0 = i > 0 ? 1u : 0u;
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint32_t d = tmem_base + kColO + 128u * g;
-          const uint32_t a_t = tmem_base + kColS + 128u * buf + 64u * g;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ts_lo(d, a_t + kk * 8, vb + ((64 * g + 16 * kk) * 128 >> 4), kIdescPV, kk == 0 ? acc0 : 1u);
-        }
-        tc_commit(&o_ready[sv]);
-      }
-      tc_commit(o_final);
-    }
-    return;
-#endif
     mbar_wait(q_full, 0, s_abort);
     if (parity == 0) WE_TRACE(13);
     if (parity == 0) { mbar_wait(&k_full[load_seq(0) % kStagesK], 0, s_abort); WE_TRACE(14); }
@@ -702,7 +673,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mbar_wait(&o_ready[ap % kStagesV], (ap / kStagesV) & 1, s_abort);
       }
       if (i == 4 || i == 5) WE_TRACE(180 + 8 * (i - 4));
-      WE_WAIT_HOT(&p_ready[buf], (i >> 1) & 1, s_abort);
+      mbar_wait(&p_ready[buf], (i >> 1) & 1, s_abort);
       if (i == 4 || i == 5) WE_TRACE(181 + 8 * (i - 4));
       tc_fence_after();
       const uint32_t vb = v_lo + sv * kTileStep;
@@ -809,7 +780,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
       const int a_i = load_seq(i);
-      WE_WAIT_HOT(&s_ready[a_i % kStagesK], (a_i / kStagesK) & 1, s_abort);
+      mbar_wait(&s_ready[a_i % kStagesK], (a_i / kStagesK) & 1, s_abort);
       if (row == 0 && i < 32 && (kFullTrace || i == 1 || i == 4 || i == 5 || i == n - 1)) WE_TRACE(16 + 4 * i + 2 * wg);
       tc_fence_after();
       uint32_t s[2][32];
@@ -1146,11 +1117,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int t = lane; t < p.T; t += 32) w[t] = 1;
     }
     // ... and its first lane issues the tensor products of the odd tiles
-#ifdef WE_ISSUE_SPLIT_KIND
-    if (lane == 0 && n > 0) issue_products(1);
-#else
     if (lane == 0 && n > 1) issue_products(1);
-#endif
     __syncwarp();
   }
 
@@ -1531,6 +1498,9 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
   p.ring_frames = static_cast<int32_t>(g->L / g->T);
   p.nsplit = sp.nsplit;
   p.n_qtiles = sp.n_qtiles;
+  p.log2_nsplit = sp.nsplit == 8 ? 3 : (sp.nsplit == 4 ? 2 : (sp.nsplit == 2 ? 1 : 0));
+  p.gqa = Hq / g->Hkv;
+  p.hid_tiles_max = g->T / kBlockN;
   p.scale_log2 = (scale > 0.f ? scale : 1.0f / sqrtf(static_cast<float>(g->Dh))) * 1.4426950408889634f;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.ws_cnt = reinterpret_cast<int32_t*>(ws);

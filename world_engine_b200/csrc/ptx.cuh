@@ -71,37 +71,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// The same with mbarrier.test_wait, which never suspends the thread: the hand-overs on the critical chain of the
-// tile loop are seen sooner than with try_wait (whose wake-up can take a few hundred cycles).
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  uint32_t it = 0;
-  while (true) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((++it & 1023u) == 0u) {
-      if (*abort_word != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_word = 1;
-        return false;
-      }
-    }
-  }
-}
-
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
