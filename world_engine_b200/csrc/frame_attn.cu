@@ -440,8 +440,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   // ---------------------------------------------------------------- set-up
   // On-chip part first: it needs nothing from global memory, so it may run while the preceding kernel of the
   // stream is still finishing (programmatic dependent launch).
-  if (tid == 0) *s_abort = 0;
   if (warp == 8) {
+    // (the abort word is cleared by the warp that is first to wait on a barrier; the others read it only after
+    // the set-up barrier below)
+    if (lane == 0) *s_abort = 0;
     // one barrier per lane: [0] q_full [1] recv_bar [2] ml_bar [3] ack_bar [4] o_final [5,6] p_ready, then
     // s_ready, o_ready, k_full, v_full
     constexpr int kNumBars = 7 + 2 * (kStagesK + kStagesV);
