@@ -133,13 +133,14 @@ WE_B200_API int we_b200_block_mask(const uint8_t* mask_written, int64_t C, int32
                        void* stream);
 
 /*
- * Bytes of zero-initialised workspace we_b200_frame_attn may need for this
- * shape on the current device (split-KV partials + arrival counters).  It is
- * only touched, and only then required, when the key splits of a query tile
- * cannot merge through cluster shared memory (splits that merge that way need
- * no workspace and the pointer may be null).  The kernel leaves the counters
- * at zero again, so one allocation zeroed once serves every later call of
- * the same or a smaller shape.
+ * Bytes of workspace we_b200_frame_attn may need for this shape on the current
+ * device (split-KV partials + arrival counters).  It is only touched, and only
+ * then required, when the key splits of a query tile cannot merge through
+ * cluster shared memory (splits that merge that way need no workspace and the
+ * pointer may be null).  Its contents need not be initialised or preserved: a
+ * launch that uses it first clears its arrival counters on `stream`, so one
+ * allocation serves calls of any shape it is large enough for, as long as they
+ * are ordered on one stream.
  */
 WE_B200_API size_t we_b200_attn_workspace_bytes(int32_t B, int32_t Hq, int32_t T, int32_t Dh, int64_t L);
 
@@ -189,8 +190,9 @@ WE_B200_API int we_b200_append_attend(const void* q, const int64_t* q_strides_ho
  * cudaMalloc / cudaFree and calls no allocating routine; inputs, output and status word are still the
  * caller's buffers.  The first call on each device looks up the array's device address (that device
  * must be current) -- make that first call before any stream capture begins.  All calls share the one
- * array: it keeps the previous call's contents (the entry point re-zeroes the small part that must
- * start at zero, on `stream`), and two calls that overlap on the GPU -- different streams, or several
+ * array: it keeps the previous call's contents (when a launch is going to use the array, the entry
+ * point first re-zeroes the small part that must start at zero, on `stream`; a call whose arguments are
+ * rejected enqueues nothing), and two calls that overlap on the GPU -- different streams, or several
  * host threads -- race on it.  Keep calls to this entry point ordered on one stream per device.
  */
 WE_B200_API int we_b200_frame_attn_static(const void* q, const int64_t* q_strides_host,

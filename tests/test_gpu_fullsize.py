@@ -43,13 +43,67 @@ def test_fullsize_step_matches_oracle_on_row_subset_and_keeps_state_exact(name):
         assert np.array_equal(cache.written.cpu().numpy(), ocache.written)
         rows = sorted({r % cfg.T for r in ROWS})
         heads = sorted({0, cfg.Hq // 2, cfg.Hq - 1})
-        kf = helpers.from_container(cfg, k_full[:1, [h * cfg.Hkv // cfg.Hq for h in heads]])
-        vf = helpers.from_container(cfg, v_full[:1, [h * cfg.Hkv // cfg.Hq for h in heads]])
-        want = oracle.frame_attention(q[:1][:, heads][:, :, rows], kf, vf, mask)
-        got = out[:1][:, heads][:, :, rows].float().cpu().numpy()
-        mx, mean = helpers.error_stats(got, want)
-        assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"{name} step {step}: max {mx} mean {mean}"
+        kv_heads = [h * cfg.Hkv // cfg.Hq for h in heads]
+        for b in range(cfg.B):                      # every batch row, a subset of query rows and heads of each
+            kf = helpers.from_container(cfg, k_full[b:b + 1, kv_heads])
+            vf = helpers.from_container(cfg, v_full[b:b + 1, kv_heads])
+            want = oracle.frame_attention(q[b:b + 1][:, heads][:, :, rows], kf, vf, mask)
+            got = out[b:b + 1][:, heads][:, :, rows].float().cpu().numpy()
+            mx, mean = helpers.error_stats(got, want)
+            assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, \
+                f"{name} step {step} batch row {b}: max {mx} mean {mean}"
         assert torch.isfinite(out.float()).all()
+    ops.check_status(torch.device("cuda"))
+
+
+def test_slab_of_64_sessions_at_random_wrap_offsets():
+    """The throughput configuration as the benchmark runs it: 64 sessions with 32-frame rings (8192 keys) in one
+    slab, every session at its own frame counter, one launch per layer-step.  Three sessions (first, middle,
+    last) are followed in the oracle: cache bytes and `written` bit-exact after a frozen and a persisting call,
+    attention on a subset of rows and heads.  The rings are filled directly (replaying 64 x 32 frames would
+    only exercise the append)."""
+    from world_engine_b200 import SessionSlab
+    from world_engine_b200.synthetic import scaled
+    base = CONFIGS["cfg4_session"]
+    S = 64
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    slab = SessionSlab(S, base.Hkv, base.L, base.Dh, torch.bfloat16, base.T)
+    slab._slab.normal_(generator=gen)
+    slab._written.fill_(True)
+    frame_ts = (32 + torch.randint(0, 10000, (S,), device="cuda", generator=gen)).tolist()
+    slab.frame_t.copy_(torch.tensor(frame_ts, device="cuda"))
+    followed = [0, 31, 63]
+    cfgs = {i: scaled(base, seed=base.seed + i, frame_t=frame_ts[i]) for i in range(S)}
+    ocaches = {}
+    for i in followed:
+        oc = helpers.new_oracle_cache(cfgs[i])
+        oc.kv[...] = slab.session_kv(i).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        oc.written[:] = True
+        ocaches[i] = oc
+    rows = sorted({r % base.T for r in ROWS})
+    heads = sorted({0, base.Hq // 2, base.Hq - 1})
+    for step, frozen in ((0, True), (1, False)):
+        qs, ks, vs = [], [], []
+        for i in range(S):
+            q, k, v = helpers.step_inputs(cfgs[i], frame_ts[i], step)
+            qs.append(q[0]); ks.append(k[0]); vs.append(v[0])
+        qd, kd, vd = (gh.dev_tensor(base, np.stack(x)) for x in (qs, ks, vs))
+        out = slab.append_and_attend(qd, kd, vd, frozen)
+        assert torch.isfinite(out.float()).all()
+        for i in followed:
+            c = cfgs[i]
+            kv_new = np.stack([helpers.to_container(c, ks[i][None]), helpers.to_container(c, vs[i][None])], 0)
+            k_full, v_full, mask = ocaches[i].upsert(kv_new, frame_ts[i], frozen)
+            assert int(mask.sum()) == c.visible_keys()
+            kv = slab.session_kv(i).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+            assert kv.tobytes() == ocaches[i].kv.tobytes(), f"session {i}: cache differs (frozen={frozen})"
+            assert np.array_equal(slab.session_written(i).cpu().numpy(), ocaches[i].written)
+            kf = helpers.from_container(c, k_full[:1, heads])
+            vf = helpers.from_container(c, v_full[:1, heads])
+            want = oracle.frame_attention(qs[i][None][:, heads][:, :, rows], kf, vf, mask)
+            got = out[i:i + 1][:, heads][:, :, rows].float().cpu().numpy()
+            mx, mean = helpers.error_stats(got, want)
+            assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"session {i} step {step}: {mx} {mean}"
     ops.check_status(torch.device("cuda"))
 
 

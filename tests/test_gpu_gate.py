@@ -1,8 +1,9 @@
 """The head gate applied inside the attention kernel (we_b200_append_attend_gated): out = attention * sigmoid(logit)
 per (batch row, head, token), src/model/attn.py:116-119.  Compared with the un-gated kernel's output times the
 gate computed by torch in fp32 (the kernel rounds once, the reference twice: a last-place difference at most), and
-with the oracle.  Shapes chosen so that every store path runs: no split, splits merged through the cluster,
-many splits, queries past the end of the last tile."""
+with the oracle's attention times the same gate.  Shapes: no split, splits merged through the cluster, many
+splits, queries past the end of the last tile (the merge through the workspace is covered by
+tests/test_gpu_workspace_merge.py, which runs these cases again)."""
 import numpy as np
 import pytest
 import torch
@@ -49,4 +50,13 @@ def test_gated_output(case, logits):
     assert bool((err <= 2 * bound).all()), f"{name}: max excess {(err - 2 * bound).max().item()}"
     assert torch.equal(caches[0].kv.view(torch.int16), caches[1].kv.view(torch.int16))
     assert torch.equal(caches[0].written, caches[1].written)
+    # against the oracle: its fp32 attention over the cache as it was (every ring frame written, this frame's slot
+    # hidden, the new frame in the tail), times the gate rounded to bf16 as the reference's `gates` tensor is
+    kv_host = caches[0].kv.float().cpu().numpy()
+    mask = np.ones(cfg.capacity, dtype=bool)
+    slot = (cfg.frame_t % ring) * T
+    mask[slot:slot + T] = False
+    want_cpu = oracle.frame_attention(q, kv_host[0], kv_host[1], mask) * factor.unsqueeze(-1).cpu().numpy()
+    mx, mean = helpers.error_stats(gated.cpu().numpy(), want_cpu)
+    assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"{name} vs oracle: max {mx} mean {mean}"
     ops.check_status(torch.device("cuda"))

@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 def test_no_alloc_entry_point_matches_the_workspace_entry_point_twice():
     # 2 rows x 4 heads x 2 query tiles = 16 units on a 148-SM part -> the KV tiles are split over several
     # CTAs.  Their partial results merge through cluster shared memory where the device can schedule such
-    # clusters and through the built-in scratch array otherwise; either way nothing is allocated.
+    # clusters and through the built-in scratch array otherwise (tests/test_gpu_workspace_merge.py runs this
+    # test once more with the merge forced through the array); either way nothing is allocated.
     cfg = StepConfig("noalloc", 2, 4, 4, 128, 256, 3, 1, 4, "bf16", 31337)
     cache = gh.new_gpu_cache(cfg)
     ocache = helpers.new_oracle_cache(cfg)
@@ -52,9 +53,10 @@ def test_no_alloc_entry_point_rejects_shapes_beyond_its_scratch():
     import ctypes
     from world_engine_b200._lib import CacheGeom, Strides3
     lib = ops._lib.load()
-    # The split-KV partials of any plan fit (their size is bounded by the SM count); what can outgrow the
-    # array is the per-unit arrival counters of a very large batch.  Nothing is launched: the pointers
-    # below are never dereferenced.
+    # What outgrows the array here is the per-unit arrival counters of a very large batch (a split plan whose
+    # partials need more than 12 MiB is rejected the same way when clusters are unavailable).  Nothing is
+    # launched: the size check comes first, and should it ever be skipped the null frame counter below makes
+    # the launcher refuse the call before any pointer is dereferenced.
     B, Hq, T, Dh, L = 65535, 64, 128, 128, 128 * 4
     need = lib.we_b200_attn_workspace_bytes(B, Hq, T, Dh, L)
     assert need > (12 << 20)
@@ -64,6 +66,6 @@ def test_no_alloc_entry_point_rejects_shapes_beyond_its_scratch():
     g.kv_batch_stride = Hq * (L + T) * Dh
     s = Strides3(Hq * T * Dh, T * Dh, Dh)
     fake = 0x10000
-    rc = lib.we_b200_frame_attn_static(fake, s, fake, s, Hq, fake, fake, fake, ctypes.byref(g), 0.0, None, None)
+    rc = lib.we_b200_frame_attn_static(fake, s, fake, s, Hq, fake, fake, None, ctypes.byref(g), 0.0, None, None)
     assert rc == -8
     assert b"12 MiB" in lib.we_b200_strerror(rc)

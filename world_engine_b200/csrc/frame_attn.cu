@@ -59,6 +59,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <type_traits>
@@ -1107,7 +1108,6 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             *reinterpret_cast<uint4*>(orow + e * 16) = v;
           }
         }
-        if (tid == 0) p.ws_cnt[unit] = 0;  // leave the counter ready for the next launch
       }
     }
   } else {
@@ -1314,16 +1314,23 @@ static int make_map(CUtensorMap* m, const void* base, int dtype, int64_t N, int6
   return r == CUDA_SUCCESS ? WE_B200_OK : WE_B200_E_DRIVER;
 }
 
+// Per-device facts are cached in atomics: several host threads may call the library at once (one per engine),
+// and the worst a race can do is ask the driver twice for the same answer.
+constexpr int kMaxDevices = 64;
+
 static int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[kMaxDevices];
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      return 148;                 // (not cached: the next call asks again)
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 struct SplitPlan {
@@ -1358,53 +1365,70 @@ static SplitPlan plan_splits(int B, int Hq, int T, int Dh, int64_t L) {
   return s;
 }
 
-// How many clusters of `cluster` CTAs of this kernel can be resident at once on the current device
-// (cached per device and cluster size; 0 = clusters of that size cannot be launched).
+// The opt-in shared-memory size of a kernel variant is set once per device.
 template <int DH, bool BF16>
-static int max_active_clusters(int cluster) {
-  static int cached[64][9];
-  static bool known[64][9] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return 0;
-  if (!known[dev][cluster]) {
-    using Cfg = AttnCfg<DH>;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(cluster) * 64u, 1, 1);
-    cfg.blockDim = dim3(kAttnThreads, 1, 1);
-    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, frame_attn_kernel<DH, BF16>, &cfg) != cudaSuccess) {
-      (void)cudaGetLastError();
-      n = 0;
-    }
-    cached[dev][cluster] = n;
-    known[dev][cluster] = true;
+static cudaError_t ensure_smem_attribute(int dev) {
+  static std::atomic<bool> done[kMaxDevices];
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  if (done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+  const cudaError_t e = cudaFuncSetAttribute(frame_attn_kernel<DH, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             AttnCfg<DH>::kSmemBytes);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return e;
   }
-  return cached[dev][cluster];
+  done[dev].store(true, std::memory_order_release);
+  return cudaSuccess;
+}
+
+// How many clusters of `cluster` CTAs of this kernel can be resident at once on the current device
+// (cached per device and cluster size; 0 = clusters of that size cannot be launched; a failed query is
+// reported as 0 but not cached).
+template <int DH, bool BF16>
+static int max_active_clusters(int dev, int cluster) {
+  static std::atomic<int> cached[kMaxDevices][9];   // value + 1; 0 = not asked yet
+  if (dev < 0 || dev >= kMaxDevices || cluster < 1 || cluster > 8) return 0;
+  const int have = cached[dev][cluster].load(std::memory_order_relaxed);
+  if (have != 0) return have - 1;
+  if (ensure_smem_attribute<DH, BF16>(dev) != cudaSuccess) return 0;   // the query needs the opt-in size set
+  using Cfg = AttnCfg<DH>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(cluster) * 64u, 1, 1);
+  cfg.blockDim = dim3(kAttnThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, frame_attn_kernel<DH, BF16>, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  cached[dev][cluster].store(n + 1, std::memory_order_relaxed);
+  return n;
 }
 
 // Can the splits of a query tile merge through cluster shared memory for this kernel variant?
+// Setting the environment variable WE_B200_FORCE_WORKSPACE_MERGE to a non-empty value other than "0" answers
+// "no" for every split plan: the splits then merge through the caller's workspace, the path a device takes on
+// which clusters of that size cannot be scheduled.  (For testing that path on devices where they can.)
 static bool cluster_merge_available(int Dh, int dtype, int nsplit) {
   if (nsplit == 1) return true;
   if (nsplit > 8) return false;
+  const char* force = getenv("WE_B200_FORCE_WORKSPACE_MERGE");
+  if (force != nullptr && force[0] != '\0' && !(force[0] == '0' && force[1] == '\0')) return false;
   int dev = 0;
-  cudaGetDevice(&dev);
-  // the occupancy query needs the opt-in shared-memory size set first
-  auto prep = [&](auto kernel, int smem) {
-    static_cast<void>(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  };
-  if (Dh == 128 && dtype == WE_B200_BF16) { prep(frame_attn_kernel<128, true>, AttnCfg<128>::kSmemBytes); return max_active_clusters<128, true>(nsplit) >= 1; }
-  if (Dh == 128) { prep(frame_attn_kernel<128, false>, AttnCfg<128>::kSmemBytes); return max_active_clusters<128, false>(nsplit) >= 1; }
-  if (dtype == WE_B200_BF16) { prep(frame_attn_kernel<64, true>, AttnCfg<64>::kSmemBytes); return max_active_clusters<64, true>(nsplit) >= 1; }
-  prep(frame_attn_kernel<64, false>, AttnCfg<64>::kSmemBytes);
-  return max_active_clusters<64, false>(nsplit) >= 1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (Dh == 128) {
+    return (dtype == WE_B200_BF16 ? max_active_clusters<128, true>(dev, nsplit)
+                                  : max_active_clusters<128, false>(dev, nsplit)) >= 1;
+  }
+  return (dtype == WE_B200_BF16 ? max_active_clusters<64, true>(dev, nsplit)
+                                : max_active_clusters<64, false>(dev, nsplit)) >= 1;
 }
 
 template <int DH, bool BF16>
@@ -1412,15 +1436,10 @@ static int launch_variant(const CUtensorMap& tq, const CUtensorMap& tk, const CU
                           const CUtensorMap& tvn, AttnParams p, dim3 grid, bool overlap_previous_kernel,
                           cudaStream_t stream) {
   using Cfg = AttnCfg<DH>;
-  static bool attr_done[64] = {false};
   int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(frame_attn_kernel<DH, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               Cfg::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_done[dev] = true;
-  }
+  cudaError_t e0 = cudaGetDevice(&dev);
+  if (e0 == cudaSuccess) e0 = ensure_smem_attribute<DH, BF16>(dev);
+  if (e0 != cudaSuccess) return static_cast<int>(e0);
   // p.cluster_merge was decided by the caller (cluster_merge_available)
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
@@ -1551,6 +1570,13 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
     p.is_frozen = fa->is_frozen ? 1 : 0;
     p.written_w = fa->written_w;
   }
+  if (!cluster_ok && sp.nsplit > 1) {
+    // The workspace keeps whatever an earlier call left in it, and a call of another shape lays its partial
+    // results where this one has its arrival counters: clear the counters on the caller's stream, now that every
+    // argument has been accepted and a launch will follow.
+    const cudaError_t e = cudaMemsetAsync(workspace, 0, sp.cnt_bytes, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   dim3 grid(static_cast<unsigned>(sp.n_qtiles * sp.nsplit), static_cast<unsigned>(Hq), static_cast<unsigned>(g->B));
   if (g->Dh == 128) {
     return g->dtype == WE_B200_BF16 ? launch_variant<128, true>(tq, tk, tv, tkn, tvn, p, grid, after_append, stream)
@@ -1592,7 +1618,10 @@ extern "C" int we_b200_frame_attn(const void* q, const int64_t* q_strides_host, 
 // part of the loaded library image: every GPU that loads the library holds these bytes until the
 // process exits, which is why the array is kept modest.
 namespace we {
-constexpr size_t kStaticScratchBytes = 12u << 20;  // 12 MiB: covers every split-KV plan on a 148-SM part at Dh <= 128
+// 12 MiB: enough for the split plans of the layer shapes this library is built for (B x heads x query tiles up to
+// a few hundred units of 8 splits at Dh = 128).  The scratch is only touched when the splits cannot merge through
+// cluster shared memory; plans that would then need more are rejected with WE_B200_E_STATIC_SCRATCH.
+constexpr size_t kStaticScratchBytes = 12u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 }  // namespace we
 
@@ -1604,11 +1633,11 @@ extern "C" int we_b200_frame_attn_static(const void* q, const int64_t* q_strides
   // In host code `g_static_scratch` is only a handle for the symbol, not a device address: the address
   // on the current device has to be asked for, once per device, with that device current.
   static std::mutex mu;
-  static void* scratch_of_device[64] = {nullptr};
+  static void* scratch_of_device[we::kMaxDevices] = {nullptr};
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 0 || dev >= 64) return WE_B200_E_LIMIT;
+  if (dev < 0 || dev >= we::kMaxDevices) return WE_B200_E_LIMIT;
   void* scratch = nullptr;
   {
     std::lock_guard<std::mutex> lock(mu);
@@ -1627,11 +1656,9 @@ extern "C" int we_b200_frame_attn_static(const void* q, const int64_t* q_strides
   if (sp.o_bytes + sp.ml_bytes + sp.cnt_bytes > we::kStaticScratchBytes &&
       !we::cluster_merge_available(geom_host->Dh, geom_host->dtype, sp.nsplit))
     return WE_B200_E_STATIC_SCRATCH;   // the splits would have to merge through more scratch than the array holds
-  // The array keeps whatever the previous call left.  Only the arrival counters must start at zero (the
-  // kernel restores them, but a call that was cut short may not have): clear them on the caller's stream.
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  e = cudaMemsetAsync(scratch, 0, sp.cnt_bytes, s);
-  if (e != cudaSuccess) return static_cast<int>(e);
+  // Every other argument is checked by the launcher before anything is enqueued; it also clears the arrival
+  // counters at the head of the scratch when (and only when) the launch is going to use them.
   return we::frame_attn_launch(q, q_strides_host, out, out_strides_host, Hq, kv, written, frame_t, geom_host, scale,
-                               scratch, we::kStaticScratchBytes, status, false, nullptr, s);
+                               scratch, we::kStaticScratchBytes, status, false, nullptr,
+                               static_cast<cudaStream_t>(stream), nullptr);
 }
