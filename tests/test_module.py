@@ -198,11 +198,15 @@ def test_module_with_table_rope_uses_the_one_pass_prologue_and_agrees_with_the_t
 
 
 @pytest.mark.gpu
-def test_module_traces_as_one_graph_with_the_custom_ops():
-    """The reference runs its model under torch.compile(fullgraph=True) (src/world_engine.py:139,148).  The
-    module must trace into ONE graph: custom ops with fake implementations and declared mutations, no host
-    synchronisation, the frame counter read on the device.  Checked with the ahead-of-time tracing backend
-    (no code generation): same outputs and same cache state as the eager module."""
+@pytest.mark.parametrize("how", ["aot_eager", "inductor", "inductor_max_autotune_no_cudagraphs"])
+def test_module_traces_as_one_graph_with_the_custom_ops(how):
+    """The reference runs its model under torch.compile(fullgraph=True, mode="max-autotune", dynamic=False)
+    (src/world_engine.py:139,148).  The module must trace into ONE graph: custom ops with fake implementations
+    and declared mutations, no host synchronisation, the frame counter read on the device.  Checked with the
+    ahead-of-time tracing backend (no code generation: bit-identical to eager) and with Inductor, in its default
+    mode and in the reference's autotuning mode without the CUDA-graph wrapper.  The custom ops are opaque to
+    Inductor; the projections and pointwise code around them are compiled, so there the outputs and the K / V
+    rows that reach the cache agree with eager to the rounding of a few elements in the last place."""
     torch.manual_seed(13)
     cfg = _Cfg()
     dev = "cuda"
@@ -224,7 +228,13 @@ def test_module_traces_as_one_graph_with_the_custom_ops():
     def step(mod, cache, x, pos, v1):
         return mod(x, pos, v1, cache)
 
-    compiled = torch.compile(step, fullgraph=True, backend="aot_eager")
+    torch._dynamo.reset()
+    if how == "aot_eager":
+        compiled = torch.compile(step, fullgraph=True, backend="aot_eager")
+    elif how == "inductor":
+        compiled = torch.compile(step, fullgraph=True, dynamic=False)
+    else:
+        compiled = torch.compile(step, fullgraph=True, dynamic=False, mode="max-autotune-no-cudagraphs")
     v1a = v1b = None
     for t, frozen in ((0, False), (1, True), (1, False), (2, False)):
         for c in caches:
@@ -235,6 +245,13 @@ def test_module_traces_as_one_graph_with_the_custom_ops():
         with torch.no_grad():
             ya, v1a = step(eager, caches[0], x, pos, v1a)
             yb, v1b = compiled(eager, caches[1], x, pos, v1b)
-        assert torch.equal(ya, yb), f"frame {t}: traced output differs from eager"
-        assert torch.equal(caches[0].layers[0].kv.view(torch.int16), caches[1].layers[0].kv.view(torch.int16))
+        ka, kb = caches[0].layers[0].kv, caches[1].layers[0].kv
+        if how == "aot_eager":
+            assert torch.equal(ya, yb), f"frame {t}: traced output differs from eager"
+            assert torch.equal(ka.view(torch.int16), kb.view(torch.int16))
+        else:
+            err = (ya.float() - yb.float()).abs()
+            assert err.max().item() <= 3e-2 and err.mean().item() <= 1e-3, (how, t, err.max().item(), err.mean().item())
+            assert (ka.float() - kb.float()).abs().max().item() <= 2 ** -4     # bf16 units in the last place, |x| <= 8
+            assert float((ka != kb).float().mean()) <= 2e-2
         assert torch.equal(caches[0].layers[0].written, caches[1].layers[0].written)

@@ -81,6 +81,12 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #ifndef WE_POLY_EVERY
 #define WE_POLY_EVERY 4
 #endif
+// Every wait of the kernel goes through this macro; debug builds record the source line of a wait that gave up.
+#ifdef WE_ATTN_DEBUG
+#define WE_WAIT(...) mbar_wait(__VA_ARGS__, s_abort, kWaitLimitNs, kWaitMinPolls, __LINE__)
+#else
+#define WE_WAIT(...) mbar_wait(__VA_ARGS__, s_abort)
+#endif
 constexpr int kPolyEvery = WE_POLY_EVERY;  // one pair of exponentials in this many runs on the FMA pipe (0: none)
 
 template <int DH>
@@ -357,6 +363,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint64_t* o_ready = s_ready + kStagesK;       // [kStagesV]
   uint64_t* k_full = o_ready + kStagesV;        // [kStagesK]
   uint64_t* v_full = k_full + kStagesK;         // [kStagesV]
+  uint64_t* drained = v_full + kStagesV;        // single phase: the stages of unneeded early loads have been released
   uint16_t* s_list = reinterpret_cast<uint16_t*>(bars + 64);          // [kMaxTiles] (tile << 1) | partial
   uint32_t* s_misc = reinterpret_cast<uint32_t*>(s_list + kMaxTiles);
   uint32_t* s_tmem = s_misc + 0;
@@ -446,8 +453,8 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // the set-up barrier below)
     if (lane == 0) *s_abort = 0;
     // one barrier per lane: [0] q_full [1] recv_bar [2] ml_bar [3] ack_bar [4] o_final [5,6] p_ready, then
-    // s_ready, o_ready, k_full, v_full
-    constexpr int kNumBars = 7 + 2 * (kStagesK + kStagesV);
+    // s_ready, o_ready, k_full, v_full, drained
+    constexpr int kNumBars = 8 + 2 * (kStagesK + kStagesV);
     static_assert(kNumBars <= 32, "one lane per barrier");
     if (lane < kNumBars) {
       const int peers = p.nsplit > 1 ? p.nsplit - 1 : 1;
@@ -623,7 +630,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (i < n_vis_blind) return (i == 0 && (blind_vis & 1u)) ? 0 : 1;   // kBlind == 2
     return i + (nblind - n_vis_blind);
   };
-  if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); }
+  if (tid == 0) { WE_TRACE(2); WE_TRACE_VAL(3, n); WE_TRACE_VAL(231, blind_vis | (nblind << 8) | (np << 16)); }
 
   // Tensor products of the tiles of one parity (thread 0 of warp 9: even tiles, of warp 11: odd tiles):
   //   S(i) = Q K(i)^T      M=128 queries, N=128 keys, K=DH in steps of 16, both operands in shared memory
@@ -644,7 +651,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     auto issue_s = [&](int i) {
       const int a = load_seq(i);
       const int sk = a % kStagesK;
-      mbar_wait(&k_full[sk], (a / kStagesK) & 1, s_abort);
+      WE_WAIT(&k_full[sk], (a / kStagesK) & 1);
       const uint32_t d = tmem_base + kColS + 128u * (i & 1);
       const uint32_t kb = k_lo + sk * kTileStep;
       umma_ss_lo<0>(d, q_lo, kb, kIdescS);
@@ -656,9 +663,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       tc_commit(&s_ready[sk]);        // the softmax warps are waiting for this one; it also frees the K stage
     };
-    mbar_wait(q_full, 0, s_abort);
+    WE_TRACE_VAL(210 + parity, 900);
+    if (parity != 0) WE_WAIT(drained, 0);
+    WE_WAIT(q_full, 0);
+    WE_TRACE_VAL(210 + parity, 901);
     if (parity == 0) WE_TRACE(13);
-    if (parity == 0) { mbar_wait(&k_full[load_seq(0) % kStagesK], 0, s_abort); WE_TRACE(14); }
+    if (parity == 0) { WE_WAIT(&k_full[load_seq(0) % kStagesK], 0); WE_TRACE(14); }
     issue_s(parity);
     if (parity == 0) WE_TRACE(15);
     for (int i = parity; i < n; i += 2) {
@@ -666,17 +676,22 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int sv = av % kStagesV;
       const int buf = i & 1;
       // everything that is ready long before P(i) is waited for first
-      mbar_wait(&v_full[sv], (av / kStagesV) & 1, s_abort);
+      WE_TRACE_VAL(210 + parity, 1000 + 10 * i + 1);
+      WE_WAIT(&v_full[sv], (av / kStagesV) & 1);
+      WE_TRACE_VAL(210 + parity, 1000 + 10 * i + 2);
       if (i + 2 < n) {
         const int a2 = load_seq(i + 2);
-        mbar_wait(&k_full[a2 % kStagesK], (a2 / kStagesK) & 1, s_abort);
+        WE_WAIT(&k_full[a2 % kStagesK], (a2 / kStagesK) & 1);
       }
+      WE_TRACE_VAL(210 + parity, 1000 + 10 * i + 3);
       if (i > 0) {
         const int ap = load_seq(i - 1);
-        mbar_wait(&o_ready[ap % kStagesV], (ap / kStagesV) & 1, s_abort);
+        WE_WAIT(&o_ready[ap % kStagesV], (ap / kStagesV) & 1);
       }
       if (i == 4 || i == 5) WE_TRACE(180 + 8 * (i - 4));
-      mbar_wait(&p_ready[buf], (i >> 1) & 1, s_abort);
+      WE_TRACE_VAL(210 + parity, 1000 + 10 * i + 4);
+      WE_WAIT(&p_ready[buf], (i >> 1) & 1);
+      WE_TRACE_VAL(210 + parity, 1000 + 10 * i + 5);
       if (i == 4 || i == 5) WE_TRACE(181 + 8 * (i - 4));
       tc_fence_after();
       const uint32_t vb = v_lo + sv * kTileStep;
@@ -714,8 +729,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       };
       for (int a = nblind; a < nloads; ++a) {
         const int st = a % stages;
+        WE_TRACE_VAL(208 + (is_k ? 0 : 1), 100 + a);
         if (a >= stages) {
-          mbar_wait(&empty[st], ((a / stages) - 1) & 1, s_abort);
+          WE_WAIT(&empty[st], ((a / stages) - 1) & 1);
           if (storer) {
             // the tile that leaves the stage belongs to the new frame: persist it before the stage is refilled
             const int kp = key_of(a - stages);
@@ -735,14 +751,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const int kp = key_of(a);
           if (kp >= p.L) {
             const int st = a % stages;
-            mbar_wait(&full[st], (a / stages) & 1, s_abort);
+            WE_WAIT(&full[st], (a / stages) & 1);
             store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
           }
         }
         bulk_commit_group();
         bulk_wait_group_read0();
       }
-      if (is_k && n == 0) mbar_wait(q_full, 0, s_abort);  // nobody else consumes Q: let the copy land before exit
+      if (is_k && n == 0) WE_WAIT(q_full, 0);  // nobody else consumes Q: let the copy land before exit
     }
     __syncwarp();
     // the rings are no longer read by stores of this warp: the epilogue may lay its exchange buffers over them
@@ -753,12 +769,20 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // tiles fetched ahead of time that hold no visible key: let them land, then free their stages
       for (int j = 0; j < nblind; ++j) {
         if (!((blind_vis >> j) & 1u)) {
-          mbar_wait(&k_full[j], 0, s_abort);
+          WE_TRACE_VAL(210, 1 + 10 * j);
+          WE_WAIT(&k_full[j], 0);
           mbar_arrive(&s_ready[j]);
-          mbar_wait(&v_full[j], 0, s_abort);
+          WE_TRACE_VAL(210, 2 + 10 * j);
+          WE_WAIT(&v_full[j], 0);
           mbar_arrive(&o_ready[j]);
+          WE_TRACE_VAL(210, 3 + 10 * j);
         }
       }
+      // The other issuing thread waits for this before its first barrier wait: a wait for the second phase of a
+      // stage barrier would pass at once while that barrier is still in its first phase (the early load has not
+      // landed yet), and the product issued on it would then complete the phase that belongs to the release
+      // above.
+      mbar_arrive(drained);
     }
     if (lane == 0 && n > 0) issue_products(0);
     __syncwarp();
@@ -783,7 +807,9 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int buf = i & 1;
       const uint32_t s_addr = tmem_base + lane_base + kColS + 128u * buf + 64u * wg;
       const int a_i = load_seq(i);
-      mbar_wait(&s_ready[a_i % kStagesK], (a_i / kStagesK) & 1, s_abort);
+      if (row == 0) WE_TRACE_VAL(212 + wg, 10 * i + 1);
+      WE_WAIT(&s_ready[a_i % kStagesK], (a_i / kStagesK) & 1);
+      if (row == 0) WE_TRACE_VAL(212 + wg, 10 * i + 2);
       if (row == 0 && i < 32 && (kFullTrace || i == 1 || i == 4 || i == 5 || i == n - 1)) WE_TRACE(16 + 4 * i + 2 * wg);
       tc_fence_after();
       uint32_t s[2][32];
@@ -890,7 +916,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // O_g is rescaled in place: PV(i-1) must have completed.  (Waiting only here is safe: the phase after
         // this one on the same barrier belongs to PV(i+1), which cannot complete before P(i+1) exists.)
         const int a_p = load_seq(i - 1);
-        mbar_wait(&o_ready[a_p % kStagesV], (a_p / kStagesV) & 1, s_abort);
+        WE_WAIT(&o_ready[a_p % kStagesV], (a_p / kStagesV) & 1);
         {
           tc_fence_after();
 #pragma unroll 1
@@ -919,7 +945,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // scheduled from here on; it waits for this grid to complete before it touches memory.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (n > 0) {
-      mbar_wait(o_final, 0, s_abort);   // (the per-tile barriers of the other group were never followed here)
+      WE_WAIT(o_final, 0);   // (the per-tile barriers of the other group were never followed here)
       tc_fence_after();
     }
     if (row == 0) WE_TRACE(224 + wg);
@@ -1153,7 +1179,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (courier) {
         const int d = warp;
         // once all peers' pairs are here their main loops are over, so their V rings may be written
-        mbar_wait(ml_bar, 0, s_abort);
+        WE_WAIT(ml_bar, 0);
         const int my_slot = split < d ? split : split - 1;          // my position among d's peers
         const uint32_t dst = dsmem_addr(smem_u32(recv) + static_cast<uint32_t>(my_slot * R * kRowB),
                                         static_cast<uint32_t>(d));
@@ -1162,7 +1188,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       // (asynchronous stores and bulk copies complete on the barrier through the async proxy, like any TMA
       // copy: the ordinary wait of the receiving CTA orders the data)
-      mbar_wait(ml_bar, 0, s_abort);           // all pairs present
+      WE_WAIT(ml_bar, 0);           // all pairs present
       if (tid == 0) WE_TRACE(242);
       // 2 NS threads share one of the R = 128 / NS rows; each takes every (2 NS)-th group of 8 columns (eight
       // neighbouring lanes read one 128-byte line: no bank conflicts).  Split u's half row enters with the weight
@@ -1187,7 +1213,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
       for (int u = 0; u < NS; ++u) w_u[u] *= inv;
       if (tid == 0) WE_TRACE(239);
-      mbar_wait(recv_bar, 0, s_abort);         // the rows of all peers have landed
+      WE_WAIT(recv_bar, 0);         // the rows of all peers have landed
       if (tid == 0) WE_TRACE(237);
       // acknowledge to the sender: its staging buffer is no longer read
       if (courier) mbar_arrive_remote(dsmem_addr(smem_u32(ack_bar), static_cast<uint32_t>(warp)));
@@ -1242,7 +1268,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (tid == kAttnThreads - 1) WE_TRACE(241);
     // This CTA may leave once every peer has acknowledged the rows pushed to it; nothing else of this CTA is
     // touched by a peer after that (their pairs and rows arrived before this CTA summed).
-    mbar_wait(ack_bar, 0, s_abort);
+    WE_WAIT(ack_bar, 0);
   }
 
   // --------------------------------------------------------------- teardown
@@ -1250,7 +1276,12 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __syncthreads();
   if (tid == 0) WE_TRACE(228);
   if (*s_abort != 0) {
+    if (tid == 0) WE_TRACE_VAL(229, *s_abort);
+#ifdef WE_ATTN_DEBUG
+    if (tid == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_WAIT_EXPIRED | (*s_abort << 8));
+#else
     if (tid == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_WAIT_EXPIRED);
+#endif
     __nanosleep(1000000);  // let copies and MMAs that are still in flight land before the CTA goes away
     __syncthreads();
   }

@@ -1,8 +1,8 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernel uses:
 // mbarrier, TMA (cp.async.bulk.tensor), tcgen05 (alloc / mma / commit / ld / st).
-// Every wait is bounded: it gives up after a wall-clock limit, records that in
-// a CTA-wide abort word, and from then on every other wait of the CTA returns
-// at once so the CTA can free its tensor memory and exit.
+// Every wait is bounded: it gives up after a limit (polls and wall clock), records
+// that in a CTA-wide abort word, and from then on every other wait of the CTA
+// returns at once so the CTA can free its tensor memory and exit.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -51,11 +51,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wall-clock limit of one wait.  A healthy kernel waits microseconds.
+// Limits of one wait.  A healthy kernel waits microseconds.  A wait gives up only when BOTH have run out: the
+// wall clock alone would also count the time during which the GPU ran another context (time slicing with
+// another process: the kernel is suspended, the clock is not), and would then report a hang that never was;
+// the polls alone have no fixed duration.  A suspended kernel polls nothing, so the poll count bounds the
+// false alarms and the wall clock bounds the patience.
 constexpr uint64_t kWaitLimitNs = 200ull * 1000ull * 1000ull;
+constexpr uint32_t kWaitMinPolls = 1u << 16;   // a failed poll blocks for about 1.5 us: some 100 ms of polling
 
 // Returns true when the phase completed, false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+// (`site` tells waits apart in the abort word; debug builds pass it on in the upper bits of the status word.)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
+                                          uint64_t limit_ns = kWaitLimitNs, uint32_t min_polls = kWaitMinPolls,
+                                          int site = 1) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   uint32_t it = 0;
@@ -63,8 +71,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++it & 63u) == 0u) {
       if (*abort_word != 0) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
-        *abort_word = 1;
+      if (it >= min_polls && global_timer_ns() - t0 > limit_ns) {
+        *abort_word = site;
         return false;
       }
     }

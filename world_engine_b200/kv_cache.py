@@ -92,9 +92,9 @@ class B200LayerKVCache(nn.Module):
         """`upsert` without the packed [2,...] copy: k, v are [B,H,T,Dh] views."""
         t_pos = self._frame_t(pos_ids)
         self._check(k, t_pos)
-        ops.kv_append_op(self.kv, self.written, self._mask_written.view(torch.uint8), k, v, t_pos,
+        ops.kv_append_op(self.kv, self.written, self._mask_written, k, v, t_pos,
                          self.tpf, self.pinned_dilation, bool(is_frozen))
-        tables = ops.block_mask_tables(self._mask_written.view(torch.uint8), self.tpf)
+        tables = ops.block_mask_tables(self._mask_written, self.tpf)
         bm = block_mask_from_tables(tables, self._mask_written, self.tpf, self.capacity)
         k_full, v_full = self.kv.unbind(0)
         return k_full, v_full, bm
@@ -116,15 +116,15 @@ class B200LayerKVCache(nn.Module):
         t_pos = self._frame_t(pos_ids)
         self._check(k, t_pos)
         if gate is not None:
-            return ops.append_attend_gated_op(q, k, v, self.kv, self.written.view(torch.uint8), t_pos, gate,
+            return ops.append_attend_gated_op(q, k, v, self.kv, self.written, t_pos, gate,
                                               self.tpf, self.pinned_dilation, bool(is_frozen), float(scale),
                                               bool(gate_is_logits))
-        return ops.append_attend_op(q, k, v, self.kv, self.written.view(torch.uint8), t_pos,
+        return ops.append_attend_op(q, k, v, self.kv, self.written, t_pos,
                                     self.tpf, self.pinned_dilation, bool(is_frozen), float(scale))
 
     def attend(self, q: Tensor, pos_ids: Mapping[str, Tensor], scale: float = 0.0) -> Tensor:
         """Attention only (the frame must already be appended)."""
-        return ops.frame_attn_op(q, self.kv, self.written.view(torch.uint8), self._frame_t(pos_ids),
+        return ops.frame_attn_op(q, self.kv, self.written, self._frame_t(pos_ids),
                                  self.tpf, self.pinned_dilation, float(scale))
 
 

@@ -95,8 +95,9 @@ def check_status(device: torch.device) -> None:
     if st != 0:
         status_word(device).zero_()
         what = {1: "a bounded wait of the attention kernel expired; the output of that call is invalid",
-                2: "a token position points outside the RoPE table (IndexError in the reference)"}.get(st, "unknown")
-        raise RuntimeError(f"world_engine_b200: device status {st}: {what}")
+                2: "a token position points outside the RoPE table (IndexError in the reference)"}.get(st & 0xFF, "unknown")
+        where = f" (debug build: wait at source line {st >> 8})" if st >> 8 else ""
+        raise RuntimeError(f"world_engine_b200: device status {st & 0xFF}: {what}{where}")
 
 
 def kv_append_(kv: torch.Tensor, written: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,

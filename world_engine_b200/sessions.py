@@ -70,9 +70,9 @@ class SessionSlab:
     def append_and_attend(self, q: Tensor, k: Tensor, v: Tensor, is_frozen: bool, scale: float = 0.0,
                           out: Tensor | None = None) -> Tensor:
         """q [S, Hq, T, Dh], k / v [S, H, T, Dh]; session i uses frame counter `frame_t[i]`."""
-        return ops.append_attend(q, k, v, self.kv, self._written.view(torch.uint8), self.frame_t, self.tpf,
+        return ops.append_attend(q, k, v, self.kv, self._written, self.frame_t, self.tpf,
                                  self.pinned_dilation, is_frozen, scale, out=out, frame_t_stride=1)
 
     def append(self, k: Tensor, v: Tensor, is_frozen: bool) -> None:
-        ops.kv_append_(self.kv, self._written.view(torch.uint8), k, v, self.frame_t, self.tpf,
+        ops.kv_append_(self.kv, self._written, k, v, self.frame_t, self.tpf,
                        self.pinned_dilation, is_frozen, frame_t_stride=1)
