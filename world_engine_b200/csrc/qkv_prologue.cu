@@ -3,15 +3,14 @@
 //   v'  = lerp(v, v1, v_lamb)                                  torch.lerp, src/model/attn.py:105-107
 //   q'  = rope(rms_norm(q)),  k' = rope(rms_norm(k))           src/model/attn.py:109-110
 //
-// One warp per (batch row, token, head) row of Dh elements (the loads of a row
-// are issued together, then the table row, then arithmetic and stores); a lane holds the
-// pairs (x[2j], x[2j+1]) RoPE rotates -- j = 2 lane, 2 lane + 1 when Dh = 128
-// (one 8-byte load, two 4-byte stores), j = lane when Dh = 64.  The RMS
-// over the row is a warp shuffle reduction in fp32; the normalised row is
-// rounded to the tensor dtype before the rotation, as the reference
-// materialises it; products and sums of the rotation are rounded separately
-// (no fused multiply-add), as eager PyTorch does.  HBM-bound byte work:
-// every element is read once and written once.
+// A warp takes eight head rows of one token (batch row, token): the three positions and the lane's 16 bytes of
+// the cos and sin rows are fetched once per warp, every row is read and written with 16-byte accesses (Dh / 8
+// lanes per row, two or four rows per pass), and all loads of the warp are in flight before the first is used.
+// A lane holds four of the pairs (x[2j], x[2j+1]) RoPE rotates.  The RMS over the row is a shuffle reduction in
+// fp32 among the lanes of the row; the normalised row is rounded to the tensor dtype before the rotation, as the
+// reference materialises it; products and sums of the rotation are rounded separately (no fused multiply-add),
+// as eager PyTorch does.  HBM-bound byte work: every element is read once and written once.  Rows that are only
+// 8-byte (Dh = 128) or 4-byte (Dh = 64) aligned take the older one-row-per-warp kernel below.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -203,6 +202,140 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const Pr
   }
 }
 
+
+// ---------------------------------------------------------------- eight rows of one token per warp
+constexpr int kRowsPerGroup = 8;
+
+template <bool BF16, int DH>
+__global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_token_kernel(const PrologueParams p) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  constexpr int kLanesPerRow = DH / 8;                  // 16 bytes per lane
+  constexpr int kRowsPerPass = 32 / kLanesPerRow;       // 2 (Dh = 128) or 4 (Dh = 64)
+  constexpr int kPasses = kRowsPerGroup / kRowsPerPass;
+  constexpr int kHalf = DH / 2;
+  const int lane = threadIdx.x & 31;
+  const int hl = lane % kLanesPerRow;                    // lane within the row: elements [8 hl, 8 hl + 8)
+  const int hr = lane / kLanesPerRow;                    // which row of the pass
+  const int slots = p.Hq + 2 * p.Hkv;                    // q heads, k heads, v heads of a token
+  const uint32_t groups = static_cast<uint32_t>((slots + kRowsPerGroup - 1) / kRowsPerGroup);
+  const uint32_t wid = blockIdx.x * (kPrologueThreads / 32) + (threadIdx.x >> 5);
+  const uint32_t token = wid / groups;
+  if (token >= static_cast<uint32_t>(p.B) * static_cast<uint32_t>(p.T)) return;
+  const int grp = static_cast<int>(wid - token * groups);
+  const int b = static_cast<int>(token / static_cast<uint32_t>(p.T));
+  const int t = static_cast<int>(token - static_cast<uint32_t>(b) * p.T);
+
+  // ---- every load that depends on nothing but the indices: the rows, the residual rows, the positions
+  int kind[kPasses];
+  uint16_t* dst[kPasses];
+  uint4 raw[kPasses], raw1[kPasses];
+  bool rotates = false;
+#pragma unroll
+  for (int i = 0; i < kPasses; ++i) {
+    const int slot = grp * kRowsPerGroup + i * kRowsPerPass + hr;
+    kind[i] = -1;
+    raw[i] = raw1[i] = make_uint4(0u, 0u, 0u, 0u);
+    dst[i] = nullptr;
+    if (slot < slots) {
+      const int w = slot < p.Hq ? 0 : (slot < p.Hq + p.Hkv ? 1 : 2);
+      const int h = w == 0 ? slot : (w == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
+      kind[i] = w;
+      rotates = rotates || w != 2;
+      dst[i] = p.out[w] + b * p.out_s[w][0] + h * p.out_s[w][1] + t * p.out_s[w][2] + 8 * hl;
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(p.in[w]) + b * p.in_s[w][0] + h * p.in_s[w][1] +
+                            t * p.in_s[w][2] + 8 * hl;
+      raw[i] = *reinterpret_cast<const uint4*>(src);
+      if (w == 2 && p.v1 != nullptr) {
+        const uint16_t* s1 = reinterpret_cast<const uint16_t*>(p.v1) + b * p.v1_s[0] + h * p.v1_s[1] + t * p.v1_s[2] +
+                             8 * hl;
+        raw1[i] = *reinterpret_cast<const uint4*>(s1);
+      }
+    }
+  }
+  rotates = __any_sync(0xffffffffu, rotates);
+  float4 cs = make_float4(0.f, 0.f, 0.f, 0.f), sn = cs;
+  if (rotates) {
+    // the angle row of the token (RoPE.get_angles, src/model/attn.py:22-31): once per warp
+    const int64_t pb = static_cast<int64_t>(b) * p.pos_bs + t;
+    int64_t idx = p.pos[0][pb] * (static_cast<int64_t>(p.height) * p.width) + p.pos[1][pb] * p.width + p.pos[2][pb];
+    if (idx < 0 || idx >= p.table_rows) {
+      if (lane == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_INDEX_RANGE);
+      idx = idx < 0 ? 0 : p.table_rows - 1;
+    }
+    cs = *reinterpret_cast<const float4*>(p.cos_t + idx * kHalf + 4 * hl);
+    sn = *reinterpret_cast<const float4*>(p.sin_t + idx * kHalf + 4 * hl);
+  }
+  float lamb = 0.f;
+  if (p.v1 != nullptr) {
+    if (p.v_lamb_dtype == WE_B200_F32) lamb = *static_cast<const float*>(p.v_lamb);
+    else if (p.v_lamb_dtype == WE_B200_BF16) lamb = __bfloat162float(*static_cast<const __nv_bfloat16*>(p.v_lamb));
+    else lamb = __half2float(*static_cast<const __half*>(p.v_lamb));
+  }
+  const float c[4] = {cs.x, cs.y, cs.z, cs.w}, s[4] = {sn.x, sn.y, sn.z, sn.w};
+
+  // ---- arithmetic and stores
+#pragma unroll
+  for (int i = 0; i < kPasses; ++i) {
+    const uint32_t rw[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    float2 x[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) x[u] = unpack_pair<BF16>(rw[u]);
+    if (kind[i] == 2) {
+      // value residual: torch.lerp's two-sided form in fp32 (src/model/attn.py:105-107)
+      if (p.v1 != nullptr) {
+        const uint32_t r1[4] = {raw1[i].x, raw1[i].y, raw1[i].z, raw1[i].w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 e = unpack_pair<BF16>(r1[u]);
+          const float d0 = __fsub_rn(e.x, x[u].x), d1 = __fsub_rn(e.y, x[u].y);
+          if (fabsf(lamb) < 0.5f) {
+            x[u].x = __fadd_rn(x[u].x, __fmul_rn(lamb, d0));
+            x[u].y = __fadd_rn(x[u].y, __fmul_rn(lamb, d1));
+          } else {
+            const float om = __fsub_rn(1.0f, lamb);
+            x[u].x = __fsub_rn(e.x, __fmul_rn(d0, om));
+            x[u].y = __fsub_rn(e.y, __fmul_rn(d1, om));
+          }
+        }
+      }
+      uint4 o;
+      o.x = static_cast<uint32_t>(to16<BF16>(x[0].x)) | (static_cast<uint32_t>(to16<BF16>(x[0].y)) << 16);
+      o.y = static_cast<uint32_t>(to16<BF16>(x[1].x)) | (static_cast<uint32_t>(to16<BF16>(x[1].y)) << 16);
+      o.z = static_cast<uint32_t>(to16<BF16>(x[2].x)) | (static_cast<uint32_t>(to16<BF16>(x[2].y)) << 16);
+      o.w = static_cast<uint32_t>(to16<BF16>(x[3].x)) | (static_cast<uint32_t>(to16<BF16>(x[3].y)) << 16);
+      *reinterpret_cast<uint4*>(dst[i]) = o;
+    }
+    // weightless RMS norm in fp32 (src/model/nn.py:55-56), rounded to the tensor dtype.  (Every lane takes part
+    // in the shuffles; rows of other kinds and empty rows contribute to sums nobody reads.)
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) ss += x[u].x * x[u].x + x[u].y * x[u].y;
+#pragma unroll
+    for (int o = kLanesPerRow / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (kind[i] == 0 || kind[i] == 1) {
+      const float rinv = 1.0f / sqrtf(ss / static_cast<float>(DH) + p.eps);
+      uint16_t y0[4], y1[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float x0 = round16<BF16>(__fmul_rn(x[u].x, rinv)), x1 = round16<BF16>(__fmul_rn(x[u].y, rinv));
+        y0[u] = to16<BF16>(__fsub_rn(__fmul_rn(x0, c[u]), __fmul_rn(x1, s[u])));   // RoPE.forward, src/model/attn.py:37-39
+        y1[u] = to16<BF16>(__fadd_rn(__fmul_rn(x1, c[u]), __fmul_rn(x0, s[u])));
+      }
+      // dst points at element 8 hl of the row; the lane's pairs are 4 hl .. 4 hl + 3: first components go to
+      // elements [4 hl, 4 hl + 4) of the first half, second components to the same places of the second half
+      uint16_t* row0 = dst[i] - 8 * hl;
+      uint2 a, bb;
+      a.x = static_cast<uint32_t>(y0[0]) | (static_cast<uint32_t>(y0[1]) << 16);
+      a.y = static_cast<uint32_t>(y0[2]) | (static_cast<uint32_t>(y0[3]) << 16);
+      bb.x = static_cast<uint32_t>(y1[0]) | (static_cast<uint32_t>(y1[1]) << 16);
+      bb.y = static_cast<uint32_t>(y1[2]) | (static_cast<uint32_t>(y1[3]) << 16);
+      *reinterpret_cast<uint2*>(row0 + 4 * hl) = a;
+      *reinterpret_cast<uint2*>(row0 + kHalf + 4 * hl) = bb;
+    }
+  }
+}
+
 }  // namespace we
 
 extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* status, void* stream) {
@@ -271,9 +404,20 @@ extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* sta
   p.status = status;
 
   const int64_t rows = static_cast<int64_t>(a->B) * a->T * (a->Hq + 2 * a->Hkv);
-  const int64_t per_block = (kPrologueThreads / 32) * kRowsPerWarp;
-  const int64_t blocks = (rows + per_block - 1) / per_block;
-  if (blocks > 0x7FFFFFFF || rows > 0x7FFFFFFF) return WE_B200_E_LIMIT;
+  // 16-byte aligned rows (the merged-QKV slices are): eight rows of a token per warp; otherwise one row per warp
+  bool wide = true;
+  for (int i = 0; i < 7; ++i) {
+    if (ptrs[i] == nullptr) continue;
+    if (reinterpret_cast<uintptr_t>(ptrs[i]) & 15u) wide = false;
+    for (int d = 0; d < 3; ++d)
+      if (strides[i][d] & 7) wide = false;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->cos_table) | reinterpret_cast<uintptr_t>(a->sin_table)) & 15u) wide = false;
+  const int64_t groups = (a->Hq + 2 * a->Hkv + kRowsPerGroup - 1) / kRowsPerGroup;
+  const int64_t per_block = wide ? (kPrologueThreads / 32) : (kPrologueThreads / 32) * kRowsPerWarp;
+  const int64_t units = wide ? static_cast<int64_t>(a->B) * a->T * groups : rows;
+  const int64_t blocks = (units + per_block - 1) / per_block;
+  if (blocks > 0x7FFFFFFF || rows > 0x7FFFFFFF || units > 0x7FFFFFFF) return WE_B200_E_LIMIT;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
   cfg.blockDim = dim3(kPrologueThreads, 1, 1);
@@ -283,8 +427,17 @@ extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* sta
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const cudaError_t e = p.bf16 ? cudaLaunchKernelEx(&cfg, qkv_prologue_kernel<true>, p)
-                               : cudaLaunchKernelEx(&cfg, qkv_prologue_kernel<false>, p);
+  cudaError_t e;
+  if (wide && p.Dh == 128) {
+    e = p.bf16 ? cudaLaunchKernelEx(&cfg, qkv_prologue_token_kernel<true, 128>, p)
+               : cudaLaunchKernelEx(&cfg, qkv_prologue_token_kernel<false, 128>, p);
+  } else if (wide) {
+    e = p.bf16 ? cudaLaunchKernelEx(&cfg, qkv_prologue_token_kernel<true, 64>, p)
+               : cudaLaunchKernelEx(&cfg, qkv_prologue_token_kernel<false, 64>, p);
+  } else {
+    e = p.bf16 ? cudaLaunchKernelEx(&cfg, qkv_prologue_kernel<true>, p)
+               : cudaLaunchKernelEx(&cfg, qkv_prologue_kernel<false>, p);
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (e != cudaSuccess) return static_cast<int>(e);
   const cudaError_t e2 = cudaGetLastError();
