@@ -149,6 +149,10 @@ struct AttnParams {
 #ifdef WE_ATTN_DEBUG
 // Debug builds only: a per-CTA timeline (SM cycles since the CTA started) written to a caller-provided buffer.
 __device__ uint32_t* g_trace = nullptr;
+// Debug builds only: when set, the first CTA of an unsplit launch lets one wait run out on purpose -- a wait
+// with a limit of a millisecond on a barrier nobody arrives on, before the CTA has issued a single copy or
+// product -- and then goes on as any CTA does whose wait gave up: status word, teardown, tensor memory freed.
+__device__ int g_expire_test = 0;
 __device__ __forceinline__ long long trace_clock() {
   long long t;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
@@ -481,6 +485,10 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
     }
     __syncwarp();
+#ifdef WE_ATTN_DEBUG
+    if (lane == 0 && p.nsplit == 1 && blockIdx.x + blockIdx.y + blockIdx.z == 0 && g_expire_test != 0)
+      mbar_wait(ack_bar, 0, s_abort, 1000ull * 1000ull, 64u, __LINE__);   // (no split: nobody ever arrives on it)
+#endif
     named_bar_arrive(4, kAttnThreads);
   }
   if (warp == 9) {
@@ -1620,6 +1628,10 @@ int frame_attn_launch(const void* q, const int64_t* qs, void* out, const int64_t
 }  // namespace we
 
 #ifdef WE_ATTN_DEBUG
+// Switches the deliberate expiry of one wait on (non-zero) or off: see g_expire_test.
+extern "C" __attribute__((visibility("default"))) int we_b200_debug_expire_wait(int on) {
+  return static_cast<int>(cudaMemcpyToSymbol(we::g_expire_test, &on, sizeof(on)));
+}
 // Buffer of 64 x 256 uint32 for the per-CTA timeline (null switches tracing off).
 extern "C" __attribute__((visibility("default"))) int we_b200_debug_trace(uint32_t* buf) {
   return static_cast<int>(cudaMemcpyToSymbol(we::g_trace, &buf, sizeof(buf)));
