@@ -418,7 +418,8 @@ def run_ours(args):
     torch.cuda.synchronize()
     # size of a bench step: as many graph replays as last about STEP_TARGET_MS (the same number on every rank)
     probe_ms = time_graph(torch, graph_step, stream, 5) / 5
-    inner_t = torch.tensor([max(1, math.ceil(STEP_TARGET_MS / max(probe_ms, 1e-3)))], device=dev, dtype=torch.int64)
+    want = args.inner if args.inner > 0 else max(1, math.ceil(STEP_TARGET_MS / max(probe_ms, 1e-3)))
+    inner_t = torch.tensor([want], device=dev, dtype=torch.int64)
     if world > 1:
         dist.all_reduce(inner_t, op=dist.ReduceOp.MAX)
     inner = int(inner_t.item())
@@ -604,7 +605,12 @@ def run_ours(args):
 
     if rank == 0:
         hbm_peak, tc_peak, peak_kind = measured_peaks()
-        total_layer_steps = world * layer_steps_per_step * args.steps
+        # cfg2 / cfg3 / cfg5: every rank runs a replica of the workload.  cfg4: one layer-step is a layer-step of
+        # all 64 sessions, of which a rank holds its shard, so the ranks together complete one per launch round.
+        if args.workload == "cfg4":
+            total_layer_steps = layer_steps_per_step * args.steps * sessions_total / 64.0
+        else:
+            total_layer_steps = world * layer_steps_per_step * args.steps
         value = total_layer_steps / (ms * 1e-3)
         us_per_layer_step = ms * 1e3 / (layer_steps_per_step * args.steps)
         elem = 2
@@ -662,8 +668,7 @@ def run_ours(args):
             "us_per_layer_step": us_per_layer_step,
             "tflops": cfg.flops() / (us_per_layer_step * 1e-6) / 1e12,
             "sessions_total": sessions_total,
-            "sessions_frames_per_s": frames_per_s if args.workload != "cfg4" else
-                                     value / world * sessions_total / (24 * 5),
+            "sessions_frames_per_s": frames_per_s if args.workload != "cfg4" else value * 64 / (24 * 5),
             "frac_of_slower_peak": bound_s / (us_per_layer_step * 1e-6),
             "us_per_frame": (ms * 1e3 / (args.steps * inner)) if args.workload == "cfg3" else None,
             "roofline": roof,
@@ -697,6 +702,9 @@ def main():
     ap.add_argument("--gpu-baseline", action="store_true",
                     help="also time torch's Inductor-compiled flex_attention + index_copy_ append on the same caches "
                          "(cfg2 workload, rank 0); adds the Triton compile time to the run")
+    ap.add_argument("--inner", type=int, default=0,
+                    help="graph replays per step (default 0: as many as last about 6 ms); 1 keeps a run under a "
+                         "profiler short")
     ap.add_argument("--profile", action="store_true",
                     help="device-timed legs only (skips the end-to-end and CPU-baseline legs): for runs under ncu")
     args = ap.parse_args()

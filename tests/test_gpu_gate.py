@@ -57,6 +57,9 @@ def test_gated_output(case, logits):
     slot = (cfg.frame_t % ring) * T
     mask[slot:slot + T] = False
     want_cpu = oracle.frame_attention(q, kv_host[0], kv_host[1], mask) * factor.unsqueeze(-1).cpu().numpy()
+    # the attention's error budget is absolute; a plain factor is not bounded by 1 like a sigmoid and scales it
+    widen = max(1.0, float(factor.abs().max()))
     mx, mean = helpers.error_stats(gated.cpu().numpy(), want_cpu)
-    assert mx <= helpers.MAX_ABS_TOL and mean <= helpers.MEAN_ABS_TOL, f"{name} vs oracle: max {mx} mean {mean}"
+    assert mx <= widen * helpers.MAX_ABS_TOL and mean <= widen * helpers.MEAN_ABS_TOL, \
+        f"{name} vs oracle: max {mx} mean {mean} (factor up to {widen})"
     ops.check_status(torch.device("cuda"))

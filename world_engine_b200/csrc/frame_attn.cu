@@ -19,8 +19,10 @@
 //               are in-thread reductions.  Group g handles keys [64g, 64g+64)
 //               of every tile as a stream of its own: running maximum, row
 //               sum and accumulator O_g; the two streams are merged once at
-//               the end.  exp2 with the scale folded in (packed fp32 pairs for the
-//               arithmetic, ex2.approx per element); the running maximum
+//               the end.  exp2 with the scale folded in, arithmetic on packed
+//               fp32 pairs; three pairs in four go through ex2.approx, the
+//               fourth through a cubic on the FMA pipe (the special-function
+//               unit is the busiest pipe of the loop); the running maximum
 //               is raised (and O_g rescaled in tensor memory) only when it
 //               grew by more than 2^8; P (bf16/f16) overwrites the S columns
 //               the thread has consumed.
@@ -30,14 +32,20 @@
 //               With the fused append both producers also persist the tiles
 //               of the new frame that pass through their rings: tensor stores
 //               from shared memory into the tail slice and the ring slot.
-//   warp 9      MMA issuer and TMEM owner: tcgen05.mma S(i+1) = Q K^T (both
-//               operands in shared memory, K-major, 128-byte swizzle) ahead
-//               into the other S buffer, then O_g += P_g V_g for both key
-//               halves of tile i (P from tensor memory, V from shared memory
-//               as an MN-major operand).
-//   warp 11     compacts the visible-tile list; with the fused append, marks
-//               the ring slot as written.
+//   warp 9      owns tensor memory; its first thread issues the tcgen05.mma
+//               products of the even tiles: O_g += P_g V_g for both key halves
+//               of tile i (P from tensor memory, V from shared memory as an
+//               MN-major operand), then at once S(i+2) = Q K^T (both operands
+//               in shared memory, K-major, 128-byte swizzle) into the S buffer
+//               that P(i) occupied.
+//   warp 11     compacts the visible-tile list, then its first thread issues
+//               the products of the odd tiles the same way (issuing a product
+//               blocks the thread about as long as the tensor pipe works on
+//               it, so two threads keep the pipe fed); with the fused append,
+//               marks the ring slot as written.
 // Tensor memory (512 columns): S0, S1, O_0, O_1, 128 columns each.
+// A completed S product frees its K stage and a completed P V product its V
+// stage: one mbarrier each serves the softmax warps and the producer.
 //
 // The launch carries the programmatic-stream-serialization attribute: barrier
 // set-up, tensor-memory allocation and tensor-map prefetch run while the
@@ -48,13 +56,14 @@
 // tiles of a query tile are split over 2, 4 or 8 CTAs that form a thread-block
 // cluster.  After its last tile a CTA sends its rows' (max, sum) pairs to the
 // peers with asynchronous stores that complete on the peers' mbarriers,
-// stages its partial rows (relative to its own maximum) in shared memory and
-// pushes each peer the rows that peer owns with one bulk copy; the owner
-// weights the rows of all splits by exp2(m_split - m_row) / l_row and adds
-// them in split order.  No cluster-wide barrier is on that path: peers signal
-// each other through mbarriers, every wait is bounded.  Where clusters of that size
-// cannot be scheduled the partials go through the caller's workspace instead
-// and the CTA that arrives last at a ticket counter merges them.
+// stages its partial rows in shared memory (16-bit floats scaled by the row's
+// largest magnitude, which travels with the row in fp32) and pushes each peer
+// the rows that peer owns with one bulk copy; the owner weights the rows of all
+// splits by exp2(m_split - m_row) / l_row and adds them in split order.  No
+// cluster-wide barrier is on that path: peers signal each other through
+// mbarriers, every wait is bounded.  Where clusters of that size cannot be
+// scheduled the partials go through the caller's workspace instead (fp32) and
+// the CTA that arrives last at a ticket counter merges them.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
