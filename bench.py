@@ -55,8 +55,9 @@ STEP_TARGET_MS = 6.0          # a bench step is sized to last about this long on
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from the ncu capture summarised in
 # the named file under profiles/ (bytes).  The figure belongs to the kernel build the capture was taken of.
 NCU_TRAFFIC = {
-    "cfg2": {"bytes": 34.69e6, "source": "profiles/frame_attn_cfg2_ncu_full.md"},
-    "cfg3": {"bytes": 34.69e6, "source": "profiles/frame_attn_cfg2_ncu_full.md"},
+    "cfg2": {"bytes": 34.71e6, "source": "profiles/frame_attn_cfg2_ncu_full.md"},
+    "cfg3": {"bytes": 34.71e6, "source": "profiles/frame_attn_cfg2_ncu_full.md"},
+    "cfg5": {"bytes": 597.6e6, "source": "profiles/frame_attn_cfg5_ncu_full.md"},
 }
 METRIC = "frame-attn layer-steps/s (append + attention)"
 WORKLOADS = {
