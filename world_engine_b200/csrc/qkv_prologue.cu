@@ -205,9 +205,27 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const Pr
 
 // ---------------------------------------------------------------- eight rows of one token per warp
 constexpr int kRowsPerGroup = 8;
+// Threads per CTA of this kernel.  Small CTAs spread the warps evenly: the layer shape has 1536 warps for 148 SMs,
+// which CTAs of eight warps deal out as one or two CTAs per SM (8 or 16 warps), CTAs of four as two or three.
+#ifndef WE_PROLOGUE_TOKEN_THREADS
+#define WE_PROLOGUE_TOKEN_THREADS 128
+#endif
+constexpr int kTokenThreads = WE_PROLOGUE_TOKEN_THREADS;
+
+// two floats -> two 16-bit values in one word (first argument in the low half), round to nearest even
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
 
 template <bool BF16, int DH>
-__global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_token_kernel(const PrologueParams p) {
+__global__ void __launch_bounds__(kTokenThreads) qkv_prologue_token_kernel(const PrologueParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int kLanesPerRow = DH / 8;                  // 16 bytes per lane
@@ -219,12 +237,21 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_token_kernel(co
   const int hr = lane / kLanesPerRow;                    // which row of the pass
   const int slots = p.Hq + 2 * p.Hkv;                    // q heads, k heads, v heads of a token
   const uint32_t groups = static_cast<uint32_t>((slots + kRowsPerGroup - 1) / kRowsPerGroup);
-  const uint32_t wid = blockIdx.x * (kPrologueThreads / 32) + (threadIdx.x >> 5);
+  const uint32_t wid = blockIdx.x * (kTokenThreads / 32) + (threadIdx.x >> 5);
   const uint32_t token = wid / groups;
   if (token >= static_cast<uint32_t>(p.B) * static_cast<uint32_t>(p.T)) return;
   const int grp = static_cast<int>(wid - token * groups);
   const int b = static_cast<int>(token / static_cast<uint32_t>(p.T));
   const int t = static_cast<int>(token - static_cast<uint32_t>(b) * p.T);
+
+  // offsets of the token within each tensor, once per warp (the head's share is added per row)
+  int64_t in_base[3], out_base[3];
+#pragma unroll
+  for (int w = 0; w < 3; ++w) {
+    in_base[w] = b * p.in_s[w][0] + t * p.in_s[w][2] + 8 * hl;
+    out_base[w] = b * p.out_s[w][0] + t * p.out_s[w][2] + 8 * hl;
+  }
+  const int64_t v1_base = b * p.v1_s[0] + t * p.v1_s[2] + 8 * hl;
 
   // ---- every load that depends on nothing but the indices: the rows, the residual rows, the positions
   int kind[kPasses];
@@ -242,13 +269,14 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_token_kernel(co
       const int h = w == 0 ? slot : (w == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
       kind[i] = w;
       rotates = rotates || w != 2;
-      dst[i] = p.out[w] + b * p.out_s[w][0] + h * p.out_s[w][1] + t * p.out_s[w][2] + 8 * hl;
-      const uint16_t* src = reinterpret_cast<const uint16_t*>(p.in[w]) + b * p.in_s[w][0] + h * p.in_s[w][1] +
-                            t * p.in_s[w][2] + 8 * hl;
+      // (selects, not indexing: an array indexed at run time would live in local memory)
+      const int64_t ib = w == 0 ? in_base[0] : (w == 1 ? in_base[1] : in_base[2]);
+      const int64_t ob = w == 0 ? out_base[0] : (w == 1 ? out_base[1] : out_base[2]);
+      dst[i] = p.out[w] + ob + h * p.out_s[w][1];
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(p.in[w]) + ib + h * p.in_s[w][1];
       raw[i] = *reinterpret_cast<const uint4*>(src);
       if (w == 2 && p.v1 != nullptr) {
-        const uint16_t* s1 = reinterpret_cast<const uint16_t*>(p.v1) + b * p.v1_s[0] + h * p.v1_s[1] + t * p.v1_s[2] +
-                             8 * hl;
+        const uint16_t* s1 = reinterpret_cast<const uint16_t*>(p.v1) + v1_base + h * p.v1_s[1];
         raw1[i] = *reinterpret_cast<const uint4*>(s1);
       }
     }
@@ -300,10 +328,10 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_token_kernel(co
         }
       }
       uint4 o;
-      o.x = static_cast<uint32_t>(to16<BF16>(x[0].x)) | (static_cast<uint32_t>(to16<BF16>(x[0].y)) << 16);
-      o.y = static_cast<uint32_t>(to16<BF16>(x[1].x)) | (static_cast<uint32_t>(to16<BF16>(x[1].y)) << 16);
-      o.z = static_cast<uint32_t>(to16<BF16>(x[2].x)) | (static_cast<uint32_t>(to16<BF16>(x[2].y)) << 16);
-      o.w = static_cast<uint32_t>(to16<BF16>(x[3].x)) | (static_cast<uint32_t>(to16<BF16>(x[3].y)) << 16);
+      o.x = pack16<BF16>(x[0].x, x[0].y);
+      o.y = pack16<BF16>(x[1].x, x[1].y);
+      o.z = pack16<BF16>(x[2].x, x[2].y);
+      o.w = pack16<BF16>(x[3].x, x[3].y);
       *reinterpret_cast<uint4*>(dst[i]) = o;
     }
     // weightless RMS norm in fp32 (src/model/nn.py:55-56), rounded to the tensor dtype.  (Every lane takes part
@@ -315,21 +343,21 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_token_kernel(co
     for (int o = kLanesPerRow / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (kind[i] == 0 || kind[i] == 1) {
       const float rinv = 1.0f / sqrtf(ss / static_cast<float>(DH) + p.eps);
-      uint16_t y0[4], y1[4];
+      float y0[4], y1[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const float x0 = round16<BF16>(__fmul_rn(x[u].x, rinv)), x1 = round16<BF16>(__fmul_rn(x[u].y, rinv));
-        y0[u] = to16<BF16>(__fsub_rn(__fmul_rn(x0, c[u]), __fmul_rn(x1, s[u])));   // RoPE.forward, src/model/attn.py:37-39
-        y1[u] = to16<BF16>(__fadd_rn(__fmul_rn(x1, c[u]), __fmul_rn(x0, s[u])));
+        y0[u] = __fsub_rn(__fmul_rn(x0, c[u]), __fmul_rn(x1, s[u]));   // RoPE.forward, src/model/attn.py:37-39
+        y1[u] = __fadd_rn(__fmul_rn(x1, c[u]), __fmul_rn(x0, s[u]));
       }
       // dst points at element 8 hl of the row; the lane's pairs are 4 hl .. 4 hl + 3: first components go to
       // elements [4 hl, 4 hl + 4) of the first half, second components to the same places of the second half
       uint16_t* row0 = dst[i] - 8 * hl;
       uint2 a, bb;
-      a.x = static_cast<uint32_t>(y0[0]) | (static_cast<uint32_t>(y0[1]) << 16);
-      a.y = static_cast<uint32_t>(y0[2]) | (static_cast<uint32_t>(y0[3]) << 16);
-      bb.x = static_cast<uint32_t>(y1[0]) | (static_cast<uint32_t>(y1[1]) << 16);
-      bb.y = static_cast<uint32_t>(y1[2]) | (static_cast<uint32_t>(y1[3]) << 16);
+      a.x = pack16<BF16>(y0[0], y0[1]);
+      a.y = pack16<BF16>(y0[2], y0[3]);
+      bb.x = pack16<BF16>(y1[0], y1[1]);
+      bb.y = pack16<BF16>(y1[2], y1[3]);
       *reinterpret_cast<uint2*>(row0 + 4 * hl) = a;
       *reinterpret_cast<uint2*>(row0 + kHalf + 4 * hl) = bb;
     }
@@ -414,13 +442,13 @@ extern "C" int we_b200_qkv_prologue(const we_b200_prologue_args* a, int32_t* sta
   }
   if ((reinterpret_cast<uintptr_t>(a->cos_table) | reinterpret_cast<uintptr_t>(a->sin_table)) & 15u) wide = false;
   const int64_t groups = (a->Hq + 2 * a->Hkv + kRowsPerGroup - 1) / kRowsPerGroup;
-  const int64_t per_block = wide ? (kPrologueThreads / 32) : (kPrologueThreads / 32) * kRowsPerWarp;
+  const int64_t per_block = wide ? (kTokenThreads / 32) : (kPrologueThreads / 32) * kRowsPerWarp;
   const int64_t units = wide ? static_cast<int64_t>(a->B) * a->T * groups : rows;
   const int64_t blocks = (units + per_block - 1) / per_block;
   if (blocks > 0x7FFFFFFF || rows > 0x7FFFFFFF || units > 0x7FFFFFFF) return WE_B200_E_LIMIT;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
-  cfg.blockDim = dim3(kPrologueThreads, 1, 1);
+  cfg.blockDim = dim3(wide ? kTokenThreads : kPrologueThreads, 1, 1);
   cfg.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
