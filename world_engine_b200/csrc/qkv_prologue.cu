@@ -204,7 +204,10 @@ __global__ void __launch_bounds__(kPrologueThreads) qkv_prologue_kernel(const Pr
 
 
 // ---------------------------------------------------------------- eight rows of one token per warp
-constexpr int kRowsPerGroup = 8;
+#ifndef WE_PROLOGUE_ROWS_PER_WARP
+#define WE_PROLOGUE_ROWS_PER_WARP 8
+#endif
+constexpr int kRowsPerGroup = WE_PROLOGUE_ROWS_PER_WARP;
 // Threads per CTA of this kernel.  Small CTAs spread the warps evenly: the layer shape has 1536 warps for 148 SMs,
 // which CTAs of eight warps deal out as one or two CTAs per SM (8 or 16 warps), CTAs of four as two or three.
 #ifndef WE_PROLOGUE_TOKEN_THREADS
@@ -244,6 +247,16 @@ __global__ void __launch_bounds__(kTokenThreads) qkv_prologue_token_kernel(const
   const int b = static_cast<int>(token / static_cast<uint32_t>(p.T));
   const int t = static_cast<int>(token - static_cast<uint32_t>(b) * p.T);
 
+  // The positions head the longest chain of dependent loads (positions -> table row): they go out first.
+  // (v rows are not rotated: a warp whose rows are all v rows skips the tables)
+  const bool rotates = grp * kRowsPerGroup < p.Hq + p.Hkv;
+  int64_t pos_t = 0, pos_y = 0, pos_x = 0;
+  if (rotates) {
+    const int64_t pb = static_cast<int64_t>(b) * p.pos_bs + t;
+    pos_t = p.pos[0][pb];
+    pos_y = p.pos[1][pb];
+    pos_x = p.pos[2][pb];
+  }
   // offsets of the token within each tensor, once per warp (the head's share is added per row)
   int64_t in_base[3], out_base[3];
 #pragma unroll
@@ -257,7 +270,6 @@ __global__ void __launch_bounds__(kTokenThreads) qkv_prologue_token_kernel(const
   int kind[kPasses];
   uint16_t* dst[kPasses];
   uint4 raw[kPasses], raw1[kPasses];
-  bool rotates = false;
 #pragma unroll
   for (int i = 0; i < kPasses; ++i) {
     const int slot = grp * kRowsPerGroup + i * kRowsPerPass + hr;
@@ -268,7 +280,6 @@ __global__ void __launch_bounds__(kTokenThreads) qkv_prologue_token_kernel(const
       const int w = slot < p.Hq ? 0 : (slot < p.Hq + p.Hkv ? 1 : 2);
       const int h = w == 0 ? slot : (w == 1 ? slot - p.Hq : slot - p.Hq - p.Hkv);
       kind[i] = w;
-      rotates = rotates || w != 2;
       // (selects, not indexing: an array indexed at run time would live in local memory)
       const int64_t ib = w == 0 ? in_base[0] : (w == 1 ? in_base[1] : in_base[2]);
       const int64_t ob = w == 0 ? out_base[0] : (w == 1 ? out_base[1] : out_base[2]);
@@ -281,12 +292,10 @@ __global__ void __launch_bounds__(kTokenThreads) qkv_prologue_token_kernel(const
       }
     }
   }
-  rotates = __any_sync(0xffffffffu, rotates);
   float4 cs = make_float4(0.f, 0.f, 0.f, 0.f), sn = cs;
   if (rotates) {
     // the angle row of the token (RoPE.get_angles, src/model/attn.py:22-31): once per warp
-    const int64_t pb = static_cast<int64_t>(b) * p.pos_bs + t;
-    int64_t idx = p.pos[0][pb] * (static_cast<int64_t>(p.height) * p.width) + p.pos[1][pb] * p.width + p.pos[2][pb];
+    int64_t idx = pos_t * (static_cast<int64_t>(p.height) * p.width) + pos_y * p.width + pos_x;
     if (idx < 0 || idx >= p.table_rows) {
       if (lane == 0 && p.status != nullptr) atomicExch(p.status, WE_B200_ST_INDEX_RANGE);
       idx = idx < 0 ? 0 : p.table_rows - 1;
