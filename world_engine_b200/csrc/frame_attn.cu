@@ -441,15 +441,21 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(dst + ch * Cfg::kChunkBytes, tm, bar, ch * 64, x1, x2, x3);
   };
 
-  // With the fused append, the CTAs of the first query tile and first query head of a kv head also persist the
-  // tiles of the new frame that pass through their rings: one tensor store from shared memory into the tail
-  // slice and, on an unfrozen write step, one into the ring slot (LayerKVCache.upsert,
-  // src/model/kv_cache.py:138,147-150).  The stores un-swizzle on the way out, like the loads swizzled.
-  const bool storer = p.fused && qt == 0 && h == kvh * p.gqa;
+  // With the fused append, the tiles of the new frame that pass through the rings are also persisted: one tensor
+  // store from shared memory into the tail slice and, on an unfrozen write step, one into the ring slot
+  // (LayerKVCache.upsert, src/model/kv_cache.py:138,147-150).  The stores un-swizzle on the way out, like the
+  // loads swizzled.  Every CTA that walks the tiles of a kv head's new frame has them in its rings (the query
+  // tiles and query heads that share the kv head): the four jobs (K or V) x (tail or slot) are dealt out among
+  // them, because a CTA's stores slow its own products (they read the same shared memory) and, through the
+  // split merge, its cluster: all four in one CTA cost 2.4 us per launch, two cost 0.6 us.
+  const int n_sharers = p.n_qtiles * p.gqa;
+  const int sharer = qt * p.gqa + (h - kvh * p.gqa);
+  auto my_store = [&](bool is_k, int dst) { return ((is_k ? 0 : 1) + 2 * dst) % n_sharers == sharer; };
   auto store_kv_tile = [&](bool is_k, const uint8_t* src, int key0, bool to_ring, int slot_base) {
     const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
 #pragma unroll 1
     for (int dst = 0; dst < (to_ring ? 2 : 1); ++dst) {
+      if (!my_store(is_k, dst)) continue;
       const int tok = dst == 0 ? key0 : key0 - static_cast<int>(p.L) + slot_base;
       const int x1 = pick3(p.kv_perm[0], tok, kvh, b), x2 = pick3(p.kv_perm[1], tok, kvh, b),
                 x3 = pick3(p.kv_perm[2], tok, kvh, b);
@@ -545,6 +551,14 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int c1 = (n_cand * (split + 1)) >> p.log2_nsplit;
   const int np = c1 - c0;
   auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
+  // Order in which this CTA walks its candidates: the tiles of the tail frame first (only the last split has
+  // them).  They were written by the kernel just ahead (or come from k_new / v_new), so they arrive from L2
+  // rather than from DRAM; and with the fused append their copies into the cache leave the rings early in the
+  // loop instead of holding up the split merge at its end.  (The order of the tiles does not matter to the
+  // result beyond the rounding of the running sums.)
+  const int c_tail = (p.L % kBlockN == 0) ? static_cast<int>(p.L / kBlockN) - count_h : n_cand;
+  const int n_tail = max(0, c1 - max(c0, c_tail));
+  auto cand_tile = [&](int j) { return phys_tile(c0 + (j < n_tail ? np - n_tail + j : j - n_tail)); };
   constexpr int kBlind = 2;                       // tiles loaded before their visibility is known
   const int nblind = np < kBlind ? np : kBlind;
   if (warp == 8 && lane == 0) {
@@ -552,11 +566,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     // do; a miss is drained later): DRAM latency then overlaps the rest of the set-up and the scan.  K(0),
     // which the first product needs, goes first.
     WE_TRACE(11);
-    if (nblind > 0) load_kv_tile(true, sK, &k_full[0], phys_tile(c0) * kBlockN);
+    if (nblind > 0) load_kv_tile(true, sK, &k_full[0], cand_tile(0) * kBlockN);
     WE_TRACE(12);
-    if (nblind > 0) load_kv_tile(false, sV, &v_full[0], phys_tile(c0) * kBlockN);
+    if (nblind > 0) load_kv_tile(false, sV, &v_full[0], cand_tile(0) * kBlockN);
     for (int j = 1; j < nblind; ++j) {
-      const int key0 = phys_tile(c0 + j) * kBlockN;
+      const int key0 = cand_tile(j) * kBlockN;
       load_kv_tile(true, sK + j * Cfg::kTileBytes, &k_full[j], key0);
       load_kv_tile(false, sV + j * Cfg::kTileBytes, &v_full[j], key0);
     }
@@ -617,11 +631,11 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll 1
       for (int base = 0; base < np; base += 32) {
         const int j = base + lane;
-        const int c = j < np ? s_cnt[phys_tile(c0 + j) - c0_min] : 0;
+        const int c = j < np ? s_cnt[cand_tile(j) - c0_min] : 0;
         const unsigned m = __ballot_sync(0xffffffffu, c != 0);
         if (c != 0)
           s_list[n + __popc(m & ((1u << lane) - 1u))] =
-              static_cast<uint16_t>((phys_tile(c0 + j) << 1) | (c != kBlockN ? 1 : 0));
+              static_cast<uint16_t>((cand_tile(j) << 1) | (c != kBlockN ? 1 : 0));
         if (base == 0) blind_vis = m & ((1u << nblind) - 1u);
         n += __popc(m);
       }
@@ -741,46 +755,54 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int stages = is_k ? kStagesK : kStagesV;
       const int nloads = nblind + n - n_vis_blind;
       const bool to_ring = !p.is_frozen && hide_i;
+      const bool storer = p.fused && (my_store(is_k, 0) || (to_ring && my_store(is_k, 1)));
       auto key_of = [&](int a) {
-        return (a < nblind ? phys_tile(c0 + a) : (s_list[a - nblind + n_vis_blind] >> 1)) * kBlockN;
+        return (a < nblind ? cand_tile(a) : (s_list[a - nblind + n_vis_blind] >> 1)) * kBlockN;
+      };
+      // Persisting (storer CTAs): every tile of the new frame among loads [sidx, hi) is written to the cache as
+      // soon as it has landed.  Called where this thread is about to block anyway; such tiles come first in the
+      // walking order and arrive from L2, so the wait is short.
+      int sidx = 0;
+      bool reads_pending = false;     // a store may still be reading a stage
+      auto persist = [&](int hi) {
+        bool any = false;
+        for (; sidx < hi; ++sidx) {
+          const int kp = key_of(sidx);
+          if (kp < p.L) continue;
+          const int st = sidx % stages;
+          WE_WAIT(&full[st], (sidx / stages) & 1);
+          store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
+          any = true;
+        }
+        if (any) {
+          bulk_commit_group();
+          reads_pending = true;
+        }
       };
       for (int a = nblind; a < nloads; ++a) {
         const int st = a % stages;
         WE_TRACE_VAL(208 + (is_k ? 0 : 1), 100 + a);
         if (a >= stages) {
+          if (storer) persist(a);       // covers load a - stages, whose stage is refilled below
           WE_WAIT(&empty[st], ((a / stages) - 1) & 1);
-          if (storer) {
-            // the tile that leaves the stage belongs to the new frame: persist it before the stage is refilled
-            const int kp = key_of(a - stages);
-            if (kp >= p.L) {
-              store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
-              bulk_commit_group();
-              bulk_wait_group_read0();
-            }
-          }
+        }
+        if (reads_pending) {
+          bulk_wait_group_read0();
+          reads_pending = false;
         }
         if (is_k && a - nblind < 32) WE_TRACE_MMA(192 + a - nblind);
         load_kv_tile(is_k, ring + st * Cfg::kTileBytes, &full[st], key_of(a));
       }
       if (storer) {
-        // new-frame tiles still resident in the ring (the last loads): wait for them to land, persist them
-        for (int a = nloads > stages ? nloads - stages : 0; a < nloads; ++a) {
-          const int kp = key_of(a);
-          if (kp >= p.L) {
-            const int st = a % stages;
-            WE_WAIT(&full[st], (a / stages) & 1);
-            store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
-          }
-        }
-        bulk_commit_group();
-        bulk_wait_group_read0();
+        persist(nloads);
+        if (reads_pending) bulk_wait_group_read0();
       }
       if (is_k && n == 0) WE_WAIT(q_full, 0);  // nobody else consumes Q: let the copy land before exit
     }
     __syncwarp();
     // the rings are no longer read by stores of this warp: the epilogue may lay its exchange buffers over them
     named_bar_arrive(5, kSoftmaxThreads + 64);
-    if (lane == 0 && storer) bulk_wait_group0();   // global writes performed before the CTA can exit
+    if (lane == 0 && p.fused) bulk_wait_group0();  // global writes performed before the CTA can exit
   } else if (warp == 9) {
     if (lane == 0) {
       // tiles fetched ahead of time that hold no visible key: let them land, then free their stages
