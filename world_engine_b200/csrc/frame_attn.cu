@@ -28,10 +28,11 @@
 //               the thread has consumed.
 //   warp 8      producer: barrier set-up, Q load, the first two K/V tiles
 //               (fetched before their visibility is known), then the K ring.
+//               With the fused append, after the last tile of the walk it
+//               does this CTA's share of persisting the new frame: it fetches
+//               a new tile once more and writes it into the tail slice or the
+//               ring slot with a tensor store from shared memory.
 //   warp 10     V producer: the V tiles through a ring of their own.
-//               With the fused append both producers also persist the tiles
-//               of the new frame that pass through their rings: tensor stores
-//               from shared memory into the tail slice and the ring slot.
 //   warp 9      owns tensor memory; its first thread issues the tcgen05.mma
 //               products of the even tiles: O_g += P_g V_g for both key halves
 //               of tile i (P from tensor memory, V from shared memory as an
@@ -441,27 +442,26 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_load_4d(dst + ch * Cfg::kChunkBytes, tm, bar, ch * 64, x1, x2, x3);
   };
 
-  // With the fused append, the tiles of the new frame that pass through the rings are also persisted: one tensor
-  // store from shared memory into the tail slice and, on an unfrozen write step, one into the ring slot
-  // (LayerKVCache.upsert, src/model/kv_cache.py:138,147-150).  The stores un-swizzle on the way out, like the
-  // loads swizzled.  Every CTA that walks the tiles of a kv head's new frame has them in its rings (the query
-  // tiles and query heads that share the kv head): the four jobs (K or V) x (tail or slot) are dealt out among
-  // them, because a CTA's stores slow its own products (they read the same shared memory) and, through the
-  // split merge, its cluster: all four in one CTA cost 2.4 us per launch, two cost 0.6 us.
+  // With the fused append the tiles of the new frame are also persisted (LayerKVCache.upsert,
+  // src/model/kv_cache.py:138,147-150): each of them, K and V, goes into the tail slice and, on an unfrozen write
+  // step, into the ring slot: "jobs" of one tensor store each (the stores un-swizzle on the way out, like the
+  // loads swizzled).  A tensor store is slow to issue (measured: a quarter of a microsecond per 16 KB box, during
+  // which the issuing thread and the loads queued behind it wait), so the jobs are dealt out among ALL CTAs
+  // that work for the kv head (every split of every query tile and query head sharing it), one or two each, and
+  // a CTA does its jobs when its K producer has requested the last tile of the walk and would idle: it fetches
+  // the new tile once more (from L2) into the K-ring stage that frees up next and stores it from there.
+  // Nothing in this launch reads the places written (the tail tiles are read from k_new / v_new, the slot is
+  // hidden), so the order against the other CTAs does not matter.
   const int n_sharers = p.n_qtiles * p.gqa;
-  const int sharer = qt * p.gqa + (h - kvh * p.gqa);
-  auto my_store = [&](bool is_k, int dst) { return ((is_k ? 0 : 1) + 2 * dst) % n_sharers == sharer; };
-  auto store_kv_tile = [&](bool is_k, const uint8_t* src, int key0, bool to_ring, int slot_base) {
+  const int job_first = split * n_sharers + qt * p.gqa + (h - kvh * p.gqa);
+  const int job_step = p.nsplit * n_sharers;
+  auto store_new_tile = [&](bool is_k, const uint8_t* src, int tile, bool into_slot, int slot_base) {
     const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
-#pragma unroll 1
-    for (int dst = 0; dst < (to_ring ? 2 : 1); ++dst) {
-      if (!my_store(is_k, dst)) continue;
-      const int tok = dst == 0 ? key0 : key0 - static_cast<int>(p.L) + slot_base;
-      const int x1 = pick3(p.kv_perm[0], tok, kvh, b), x2 = pick3(p.kv_perm[1], tok, kvh, b),
-                x3 = pick3(p.kv_perm[2], tok, kvh, b);
+    const int tok = (into_slot ? slot_base : static_cast<int>(p.L)) + tile * kBlockN;
+    const int x1 = pick3(p.kv_perm[0], tok, kvh, b), x2 = pick3(p.kv_perm[1], tok, kvh, b),
+              x3 = pick3(p.kv_perm[2], tok, kvh, b);
 #pragma unroll
-      for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_store_4d(tm, src + ch * Cfg::kChunkBytes, ch * 64, x1, x2, x3);
-    }
+    for (int ch = 0; ch < Cfg::kChunks; ++ch) tma_store_4d(tm, src + ch * Cfg::kChunkBytes, ch * 64, x1, x2, x3);
   };
 
   // ---------------------------------------------------------------- set-up
@@ -553,8 +553,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   auto phys_tile = [&](int c) { return c < first_h ? c : c + count_h; };
   // Order in which this CTA walks its candidates: the tiles of the tail frame first (only the last split has
   // them).  They were written by the kernel just ahead (or come from k_new / v_new), so they arrive from L2
-  // rather than from DRAM; and with the fused append their copies into the cache leave the rings early in the
-  // loop instead of holding up the split merge at its end.  (The order of the tiles does not matter to the
+  // rather than from DRAM and the first product starts sooner.  (The order of the tiles does not matter to the
   // result beyond the rounding of the running sums.)
   const int c_tail = (p.L % kBlockN == 0) ? static_cast<int>(p.L / kBlockN) - count_h : n_cand;
   const int n_tail = max(0, c1 - max(c0, c_tail));
@@ -754,48 +753,36 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint64_t* empty = is_k ? s_ready : o_ready;
       const int stages = is_k ? kStagesK : kStagesV;
       const int nloads = nblind + n - n_vis_blind;
-      const bool to_ring = !p.is_frozen && hide_i;
-      const bool storer = p.fused && (my_store(is_k, 0) || (to_ring && my_store(is_k, 1)));
       auto key_of = [&](int a) {
         return (a < nblind ? cand_tile(a) : (s_list[a - nblind + n_vis_blind] >> 1)) * kBlockN;
-      };
-      // Persisting (storer CTAs): every tile of the new frame among loads [sidx, hi) is written to the cache as
-      // soon as it has landed.  Called where this thread is about to block anyway; such tiles come first in the
-      // walking order and arrive from L2, so the wait is short.
-      int sidx = 0;
-      bool reads_pending = false;     // a store may still be reading a stage
-      auto persist = [&](int hi) {
-        bool any = false;
-        for (; sidx < hi; ++sidx) {
-          const int kp = key_of(sidx);
-          if (kp < p.L) continue;
-          const int st = sidx % stages;
-          WE_WAIT(&full[st], (sidx / stages) & 1);
-          store_kv_tile(is_k, ring + st * Cfg::kTileBytes, kp, to_ring, slot_base);
-          any = true;
-        }
-        if (any) {
-          bulk_commit_group();
-          reads_pending = true;
-        }
       };
       for (int a = nblind; a < nloads; ++a) {
         const int st = a % stages;
         WE_TRACE_VAL(208 + (is_k ? 0 : 1), 100 + a);
-        if (a >= stages) {
-          if (storer) persist(a);       // covers load a - stages, whose stage is refilled below
-          WE_WAIT(&empty[st], ((a / stages) - 1) & 1);
-        }
-        if (reads_pending) {
-          bulk_wait_group_read0();
-          reads_pending = false;
-        }
+        if (a >= stages) WE_WAIT(&empty[st], ((a / stages) - 1) & 1);
         if (is_k && a - nblind < 32) WE_TRACE_MMA(192 + a - nblind);
         load_kv_tile(is_k, ring + st * Cfg::kTileBytes, &full[st], key_of(a));
       }
-      if (storer) {
-        persist(nloads);
-        if (reads_pending) bulk_wait_group_read0();
+      if (is_k && p.fused) {
+        // this CTA's share of the store jobs: job = (K or V) + 2 * (tile + tiles * (tail or slot))
+        const int tiles = p.T / kBlockN;
+        const int n_jobs = 2 * tiles * ((!p.is_frozen && hide_i) ? 2 : 1);
+        int a = nloads;                                  // the walk goes on with loads nobody multiplies
+        for (int job = job_first; job < n_jobs; job += job_step, ++a) {
+          const bool k_plane = (job & 1) == 0;
+          const int tile = (job >> 1) % tiles;
+          const bool into_slot = (job >> 1) >= tiles;
+          const int st = a % stages;
+          // the stage is free when the product that read its last tile is complete, or, when an earlier job of
+          // this loop used it (more jobs than stages), when that job's store has read it
+          if (a >= stages && a - stages < nloads && !WE_WAIT(&empty[st], ((a / stages) - 1) & 1)) break;
+          if (a - stages >= nloads) bulk_wait_group_read0();
+          load_kv_tile(k_plane, ring + st * Cfg::kTileBytes, &full[st], static_cast<int>(p.L) + tile * kBlockN);
+          if (!WE_WAIT(&full[st], (a / stages) & 1)) break;             // giving up: store nothing
+          store_new_tile(k_plane, ring + st * Cfg::kTileBytes, tile, into_slot, slot_base);
+          bulk_commit_group();
+        }
+        bulk_wait_group_read0();
       }
       if (is_k && n == 0) WE_WAIT(q_full, 0);  // nobody else consumes Q: let the copy land before exit
     }
@@ -1178,7 +1165,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   } else {
     // warp 11: with the fused append on an unfrozen write step, one CTA per batch row marks the ring slot as
     // written (LayerKVCache.upsert, src/model/kv_cache.py:151); the rows themselves are persisted by the
-    // producer warps of the CTAs whose rings they pass through.
+    // K producers of the CTAs that work for the kv head, a job or two each.
     if (p.fused && !p.is_frozen && hide_i && h == 0 && qt == 0 && split == 0) {
       uint8_t* w = p.written_w + b * p.written_batch_stride + slot_base;
       for (int t = lane; t < p.T; t += 32) w[t] = 1;
