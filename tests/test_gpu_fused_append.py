@@ -21,6 +21,8 @@ CASES = [
     ("two_tail_tiles_gqa", 1, 8, 2, 128, 256, 3, 1),
     ("dilation2", 2, 2, 2, 128, 128, 4, 2),
     ("long_tail", 2, 16, 8, 128, 512, 2, 1),   # unsplit CTAs: more new-frame tiles than ring stages in one CTA
+    # unsplit, two CTAs per kv head: four store jobs per CTA on a persisting step, more than the K ring has stages
+    ("many_jobs_per_cta", 20, 4, 4, 128, 256, 3, 1),
 ]
 
 
