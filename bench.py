@@ -57,7 +57,7 @@ STEP_TARGET_MS = 6.0          # a bench step is sized to last about this long on
 NCU_TRAFFIC = {
     "cfg2": {"bytes": 34.71e6, "source": "profiles/frame_attn_cfg2_ncu_full.md"},
     "cfg3": {"bytes": 34.71e6, "source": "profiles/frame_attn_cfg2_ncu_full.md"},
-    "cfg5": {"bytes": 597.6e6, "source": "profiles/frame_attn_cfg5_ncu_full.md"},
+    "cfg5": {"bytes": 584.9e6, "source": "profiles/frame_attn_cfg5_ncu_full.md"},
 }
 METRIC = "frame-attn layer-steps/s (append + attention)"
 WORKLOADS = {
