@@ -1366,7 +1366,7 @@ static int make_map(CUtensorMap* m, const void* base, int dtype, int64_t N, int6
   for (int i = 0; i < 3; ++i) perm[i] = ax[i].src;
   const CUtensorMapDataType dt = dtype == WE_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = fn(m, dt, 4, const_cast<void*>(base), dims, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? WE_B200_OK : WE_B200_E_DRIVER;
 }
