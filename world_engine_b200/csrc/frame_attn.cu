@@ -767,7 +767,7 @@ frame_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         // this CTA's share of the store jobs: job = (K or V) + 2 * (tile + tiles * (tail or slot))
         const int tiles = p.T / kBlockN;
         const int n_jobs = 2 * tiles * ((!p.is_frozen && hide_i) ? 2 : 1);
-        int a = nloads;                                  // the walk goes on with loads nobody multiplies
+        int a = nloads;                                  // the ring goes on with loads that no product consumes
         for (int job = job_first; job < n_jobs; job += job_step, ++a) {
           const bool k_plane = (job & 1) == 0;
           const int tile = (job >> 1) % tiles;
